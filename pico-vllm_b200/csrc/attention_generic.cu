@@ -57,7 +57,8 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ q, int q_row_stride, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ tok_seg, const int* __restrict__ positions, const int* __restrict__ block_table,
-    int table_stride, int nh, int nkv, int hd, int page_size, int window, float scale, int n_splits, float softcap) {
+    int table_stride, int nh, int nkv, int hd, int page_size, int window, float scale, int n_splits, float softcap,
+    const float* __restrict__ slopes, int chunk, const float* __restrict__ sinks) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float q_s[];  // [warps][hd]
@@ -67,7 +68,8 @@ __global__ void paged_attention_generic_kernel(
     const int seg = tok_seg[t];
     const int pos = positions[t];
     const int hi = pos + 1;
-    const int lo = (window > 0 && hi > window) ? hi - window : 0;
+    int lo = (window > 0 && hi > window) ? hi - window : 0;
+    if (chunk > 0 && pos >= 0) lo = max(lo, pos / chunk * chunk);      // only the keys of the query's own chunk of positions
     // this split's part of [lo, hi), in whole tiles of 32 keys counted from lo
     const int ntiles = (hi - lo + 31) / 32;
     const int per = (ntiles + n_splits - 1) / n_splits;
@@ -84,6 +86,7 @@ __global__ void paged_attention_generic_kernel(
         for (int d = lane; d < hd; d += 32) qw[d] = to_f32(qp[d]) * scale;
         __syncwarp();
         float m = -INFINITY, l = 0.f;
+        const float slope = slopes ? slopes[h] : 0.f;      // a distance bias: slope * (query position - key position) is taken off
         float o[ATT_MAX_DPL];
 #pragma unroll
         for (int j = 0; j < ATT_MAX_DPL; ++j) o[j] = 0.f;
@@ -98,6 +101,7 @@ __global__ void paged_attention_generic_kernel(
                 row = (((long long)page * nkv + kh) * page_size + (n % page_size)) * hd;
                 s = dot_row<T>(qw, k_pages + row, hd);
                 if (softcap > 0.f) s = softcap * tanhf(s / softcap);     // scores are bounded by +-softcap before the softmax
+                s -= slope * (float)(pos - n);
             }
             const float m_new = fmaxf(m, warp_max(s));
             const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
@@ -119,6 +123,13 @@ __global__ void paged_attention_generic_kernel(
             }
         }
         if (n_splits == 1) {
+            if (sinks) {        // one more key of score sinks[h] with no value: it only adds to the denominator
+                const float m_new = fmaxf(m, sinks[h]);
+                const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+                l = l * corr + expf(sinks[h] - m_new);
+#pragma unroll
+                for (int j = 0; j < ATT_MAX_DPL; ++j) o[j] *= corr;
+            }
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             T* op = out + ((size_t)t * nh + h) * hd;
 #pragma unroll
@@ -145,14 +156,15 @@ __global__ void paged_attention_generic_kernel(
 // out[t, h, :] = sum_i o_i exp(m_i - M) / sum_i l_i exp(m_i - M) over the splits i.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         T* __restrict__ out, int hd, int n_splits) {
+                                         T* __restrict__ out, int hd, int n_splits, const float* __restrict__ sinks,
+                                         int nh) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t th = blockIdx.x;  // t * nh + h
     const float* ml = part_ml + th * n_splits * 2;
-    float M = -INFINITY;
+    float M = sinks ? sinks[th % nh] : -INFINITY;
     for (int i = 0; i < n_splits; ++i) M = fmaxf(M, ml[2 * i]);
-    float L = 0.f;
+    float L = sinks ? expf(sinks[th % nh] - M) : 0.f;
     for (int i = 0; i < n_splits; ++i) {
         const float mi = ml[2 * i];
         if (mi != -INFINITY) L += ml[2 * i + 1] * expf(mi - M);
@@ -176,11 +188,12 @@ PICO_API int pico_paged_attention_generic(const void* q, int q_row_stride, const
                                           const int* tok_seg, const int* positions, const int* block_table,
                                           int table_stride, int T, int nh, int nkv, int hd, int page_size,
                                           int window, float scale, int n_splits, float softcap, int act_dtype,
-                                          cudaStream_t stream) {
+                                          const float* slopes, int chunk, const float* sinks, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hd % 16 != 0 || hd < 16 || hd > 32 * ATT_MAX_DPL) return PICO_ERR_SIZE;
     if (nkv <= 0 || nh % nkv != 0 || n_splits < 1 || n_splits > 65535 || nkv > 65535) return PICO_ERR_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml)) return PICO_ERR_SIZE;
+    if (chunk < 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
     const int warps = g < 4 ? g : 4;
     const dim3 grid(T, nkv, n_splits);
@@ -189,15 +202,17 @@ PICO_API int pico_paged_attention_generic(const void* q, int q_row_stride, const
         if ((q_row_stride % 4) != 0) return PICO_ERR_ALIGN;
         pico_launch((paged_attention_generic_kernel<float>), dim3(grid), dim3(warps * 32), smem, stream, 
             (const float*)q, q_row_stride, (const float*)k_pages, (const float*)v_pages, (float*)out, part_o,
-            part_ml, tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits, softcap);
+            part_ml, tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits, softcap,
+            slopes, chunk, sinks);
         if (n_splits > 1)
-            pico_launch((attention_combine_kernel<float>), dim3(T * nh), dim3(64), 0, stream, part_o, part_ml, (float*)out, hd, n_splits);
+            pico_launch((attention_combine_kernel<float>), dim3(T * nh), dim3(64), 0, stream, part_o, part_ml, (float*)out, hd, n_splits, sinks, nh);
     } else if (act_dtype == PICO_BF16) {
         pico_launch((paged_attention_generic_kernel<bf16>), dim3(grid), dim3(warps * 32), smem, stream, 
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, part_o, part_ml,
-            tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits, softcap);
+            tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits, softcap, slopes, chunk,
+            sinks);
         if (n_splits > 1)
-            pico_launch((attention_combine_kernel<bf16>), dim3(T * nh), dim3(64), 0, stream, part_o, part_ml, (bf16*)out, hd, n_splits);
+            pico_launch((attention_combine_kernel<bf16>), dim3(T * nh), dim3(64), 0, stream, part_o, part_ml, (bf16*)out, hd, n_splits, sinks, nh);
     } else
         return PICO_ERR_DTYPE;
     return pico_launch_status();
@@ -263,7 +278,7 @@ PICO_API int pico_paged_attention_noalloc(const void* q, int q_row_stride, const
     float* part_ml = part_o + (size_t)T * nh * n_splits * hd;
     const int rc = pico_paged_attention_generic(q, q_row_stride, k_pages, v_pages, out, part_o, part_ml, tok_seg,
                                                 positions, block_table, table_stride, T, nh, nkv, hd, page_size,
-                                                window, scale, n_splits, 0.f, act_dtype, stream);
+                                                window, scale, n_splits, 0.f, act_dtype, nullptr, 0, nullptr, stream);
     if (rc == PICO_ERR_SIZE) return noalloc_fail(rc, err, err_len, "a size the attention kernels do not take");
     if (rc == PICO_ERR_DTYPE) return noalloc_fail(rc, err, err_len, "act_dtype must be 0 (float32) or 1 (bfloat16)");
     if (rc == PICO_ERR_ALIGN) return noalloc_fail(rc, err, err_len, "q_row_stride must be a multiple of 4 for float32");

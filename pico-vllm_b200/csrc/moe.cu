@@ -25,17 +25,18 @@
 
 enum { MOE_GATE_UP = 0, MOE_DOWN = 1, MOE_UP_ACT = 2 };
 enum { MOE_ACT_SILU = 0, MOE_ACT_RELU2 = 1 };
-enum { MOE_SCORE_SOFTMAX_CHOSEN = 0, MOE_SCORE_SIGMOID = 1 };
+enum { MOE_SCORE_SOFTMAX_CHOSEN = 0, MOE_SCORE_SIGMOID = 1, MOE_SCORE_SOFTMAX_ALL = 2 };
 
 // TOK tokens per block (their rows of h in shared memory as float32, so that a warp reads an expert's router row once
 // for all of them); 8 warps take the experts in turn; warp w < TOK then chooses for token w.
 template <typename TA, int TOK>
 __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h, const float* __restrict__ wr,
                                                         const float* __restrict__ br, int T, int D, int E, int top,
-                                                        int mode, int* __restrict__ idx, float* __restrict__ wgt) {
+                                                        int mode, int* __restrict__ idx, float* __restrict__ wgt,
+                                                        const float* __restrict__ choice_bias, float weight_scale) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ __align__(16) float rsm[];       // TOK rows of D floats (D rounded up to 4), then TOK x E logits
+    extern __shared__ __align__(16) float rsm[];       // TOK rows of D floats (D rounded up to 4), then TOK x E logits (twice for mode 2)
     const int Dp = (D + 3) & ~3;
     float* hs = rsm;
     float* z = rsm + TOK * Dp;
@@ -80,6 +81,22 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h
     if (warp >= nt) return;
     float* zt = z + warp * E;
     const int t = t0 + warp;
+    // mode 2: the score of an expert is its share of the softmax over ALL logits; the choice is by score + choice_bias, the
+    // weight is the score itself (times weight_scale), not renormalised over the chosen
+    float* score = z + TOK * E + warp * E;
+    if (mode == MOE_SCORE_SOFTMAX_ALL) {
+        float mx = -INFINITY, den = 0.f;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zt[e]);
+        mx = warp_max(mx);
+        for (int e = lane; e < E; e += 32) den += expf(zt[e] - mx);
+        den = warp_sum(den);
+        for (int e = lane; e < E; e += 32) {
+            const float p = expf(zt[e] - mx) / den;
+            score[e] = p;
+            zt[e] = p + (choice_bias ? choice_bias[e] : 0.f);
+        }
+        __syncwarp();
+    }
     float first = 0.f, sum = 0.f, mine = 0.f;    // lane j keeps the j-th chosen logit (top <= 32)
     int mine_e = 0;
     for (int j = 0; j < top; ++j) {
@@ -97,7 +114,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h
         }
         if (be == 0x7fffffff) be = 0;           // only NaN or -inf left: keep indices legal
         if (j == 0) first = best;
-        const float p = mode == MOE_SCORE_SIGMOID ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
+        const float p = mode == MOE_SCORE_SOFTMAX_ALL ? score[be] * weight_scale
+                        : mode == MOE_SCORE_SIGMOID ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
         sum += p;
         if (lane == j) { mine = p; mine_e = be; }
         __syncwarp();
@@ -106,7 +124,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h
     }
     if (lane < top) {
         idx[(size_t)t * top + lane] = mine_e;
-        wgt[(size_t)t * top + lane] = mode == MOE_SCORE_SIGMOID ? mine : mine / sum;
+        wgt[(size_t)t * top + lane] = mode == MOE_SCORE_SOFTMAX_CHOSEN ? mine / sum : mine;
     }
 }
 
@@ -360,33 +378,38 @@ __global__ void __launch_bounds__(256) moe_gemm_simple_kernel(const TA* __restri
 
 template <typename TA>
 __global__ void moe_combine_kernel(const float* __restrict__ out2, const float* __restrict__ wgt, int top, int D,
-                                   size_t total, TA* __restrict__ y, const TA* __restrict__ base) {
+                                   size_t total, TA* __restrict__ y, const TA* __restrict__ base, const int* __restrict__ eidx,
+                                   int n_real, const TA* __restrict__ h) {
     pdl_launch_dependents();
     pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / D;
         const int d = (int)(idx - t * D);
         float acc = base ? to_f32(base[idx]) : 0.f;        // wgt nullptr: a plain sum; base: added to it (a shared expert's output)
-        for (int j = 0; j < top; ++j) acc += (wgt ? wgt[t * top + j] : 1.0f) * out2[(t * top + j) * (size_t)D + d];
+        for (int j = 0; j < top; ++j) {
+            // an entry that names an expert beyond the real ones passes the layer's input on as it is
+            const bool pass = eidx && eidx[t * top + j] >= n_real;
+            acc += (wgt ? wgt[t * top + j] : 1.0f) * (pass ? to_f32(h[idx]) : out2[(t * top + j) * (size_t)D + d]);
+        }
         y[idx] = from_f32<TA>(acc);
     }
 }
 
 // h [T, D]; wr float32 [E, D]; br float32 [E] or nullptr; idx int32 [T, top]; wgt float32 [T, top].
 PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int T, int D, int E, int top, int mode,
-                            int* idx, float* wgt, int dtype, cudaStream_t stream) {
+                            int* idx, float* wgt, int dtype, const float* choice_bias, float weight_scale, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (E < 1 || top < 1 || top > E || top > 32 || E > 8192 || mode < 0 || mode > 1) return PICO_ERR_SIZE;
+    if (E < 1 || top < 1 || top > E || top > 32 || E > 8192 || mode < 0 || mode > 2) return PICO_ERR_SIZE;
     // four tokens a block when there are many (the router matrix is read once per block), one otherwise
     const int tok = T >= 512 ? 4 : 1;
-    const size_t smem = ((size_t)tok * ((D + 3) & ~3) + (size_t)tok * E) * sizeof(float);
+    const size_t smem = ((size_t)tok * ((D + 3) & ~3) + (size_t)2 * tok * E) * sizeof(float);
     if (smem > 200 * 1024) return PICO_ERR_SIZE;
     const dim3 grid((T + tok - 1) / tok);
 #define LAUNCH_ROUTE(TA, TOK)                                                                                             \
     do {                                                                                                                  \
         if (smem > 48 * 1024)                                                                                             \
             cudaFuncSetAttribute(moe_route_kernel<TA, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-        pico_launch((moe_route_kernel<TA, TOK>), grid, dim3(256), smem, stream, (const TA*)h, wr, br, T, D, E, top, mode, idx, wgt); \
+        pico_launch((moe_route_kernel<TA, TOK>), grid, dim3(256), smem, stream, (const TA*)h, wr, br, T, D, E, top, mode, idx, wgt, choice_bias, weight_scale); \
     } while (0)
     if (dtype == PICO_F32) {
         if (tok == 4) LAUNCH_ROUTE(float, 4); else LAUNCH_ROUTE(float, 1);
@@ -448,7 +471,8 @@ PICO_API int pico_moe_gather(const void* x, const int* perm, int n, int top, int
 template <typename TA, bool VEC>
 __global__ void moe_combine_placed_kernel(const TA* __restrict__ ys, const int* __restrict__ place,
                                           const float* __restrict__ wgt, int top, int D, size_t total, TA* __restrict__ y,
-                                          const TA* __restrict__ base) {
+                                          const TA* __restrict__ base, const int* __restrict__ eidx, int n_real,
+                                          const TA* __restrict__ h) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int W = VEC ? 16 / (int)sizeof(TA) : 1;
@@ -461,7 +485,8 @@ __global__ void moe_combine_placed_kernel(const TA* __restrict__ ys, const int* 
         for (int k = 0; k < W; ++k) acc[k] = base ? to_f32(base[t * (size_t)D + d + k]) : 0.f;
         for (int j = 0; j < top; ++j) {
             const float g = wgt ? wgt[t * top + j] : 1.0f;
-            const TA* row = ys + (size_t)place[t * top + j] * D + d;
+            const bool pass = eidx && eidx[t * top + j] >= n_real;     // an expert that hands its input on
+            const TA* row = pass ? h + t * (size_t)D + d : ys + (size_t)place[t * top + j] * D + d;
             if (VEC) {
                 const uint4 raw = *reinterpret_cast<const uint4*>(row);
                 const TA* v = reinterpret_cast<const TA*>(&raw);
@@ -484,7 +509,8 @@ __global__ void moe_combine_placed_kernel(const TA* __restrict__ ys, const int* 
 }
 
 PICO_API int pico_moe_combine_placed(const void* ys, const int* place, const float* wgt, int T, int top, int D, void* y,
-                                     const void* base, int dtype, cudaStream_t stream) {
+                                     const void* base, int dtype, const int* eidx, int n_real, const void* h,
+                                     cudaStream_t stream) {
     if (T <= 0) return 0;
     if (dtype != PICO_F32 && dtype != PICO_BF16) return PICO_ERR_DTYPE;
     const int w = dtype == PICO_F32 ? 4 : 8;
@@ -495,7 +521,7 @@ PICO_API int pico_moe_combine_placed(const void* ys, const int* place, const flo
     const int blocks = (int)((long long)want > cap ? cap : (long long)want);
 #define LAUNCH_CP(TA, V)                                                                                              \
     pico_launch((moe_combine_placed_kernel<TA, V>), dim3(blocks), dim3(256), 0, stream, (const TA*)ys, place, wgt, top, D, \
-                total, (TA*)y, (const TA*)base)
+                total, (TA*)y, (const TA*)base, eidx, n_real, (const TA*)h)
     if (dtype == PICO_F32) {
         if (vec) LAUNCH_CP(float, true); else LAUNCH_CP(float, false);
     } else {
@@ -545,7 +571,7 @@ PICO_API int pico_moe_gemm(const void* a, const void* w, const int* offsets, con
 
 // out2 float32 [T * top, D]; wgt float32 [T, top]; y [T, D].
 PICO_API int pico_moe_combine(const float* out2, const float* wgt, int T, int top, int D, void* y, const void* base,
-                              int dtype, cudaStream_t stream) {
+                              int dtype, const int* eidx, int n_real, const void* h, cudaStream_t stream) {
     if (T <= 0) return 0;
     const size_t total = (size_t)T * D;
     const long long cap = 16LL * pico_num_sms();
@@ -553,10 +579,10 @@ PICO_API int pico_moe_combine(const float* out2, const float* wgt, int T, int to
     const int blocks = (int)((long long)want > cap ? cap : (long long)want);
     if (dtype == PICO_F32)
         pico_launch((moe_combine_kernel<float>), dim3(blocks), dim3(256), 0, stream, out2, wgt, top, D, total, (float*)y,
-                    (const float*)base);
+                    (const float*)base, eidx, n_real, (const float*)h);
     else if (dtype == PICO_BF16)
         pico_launch((moe_combine_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, out2, wgt, top, D, total, (bf16*)y,
-                    (const bf16*)base);
+                    (const bf16*)base, eidx, n_real, (const bf16*)h);
     else
         return PICO_ERR_DTYPE;
     return pico_launch_status();

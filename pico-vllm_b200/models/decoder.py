@@ -11,10 +11,11 @@ wanted rows only.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
+from .. import ops
 from ..errors import ConfigError
 from ..parts.base import CacheView, Part
 
@@ -22,7 +23,8 @@ from ..parts.base import CacheView, Part
 @dataclass(frozen=True)
 class LayerCall:
     block: int                 # index into DecoderModel.blocks
-    cache: Optional[int]       # index of the cache entry this call uses (None: the mixer keeps nothing)
+    cache: Union[None, int, Tuple[int, ...]]   # the cache entry this call uses (None: the mixer keeps nothing); a tuple
+                               # for a mixer whose cache_spec() is a tuple of needs: one entry for each, in order
     store: bool = True         # False: read an entry that an earlier call of the order fills
 
 
@@ -34,12 +36,15 @@ class Binding:
 
 class DecoderModel:
     def __init__(self, config, embed: Part, blocks: Sequence, order: Sequence[LayerCall], final_norm: Part,
-                 head: Part, bindings: List[Binding], embed_position: Optional[Part] = None):
+                 head: Part, bindings: List[Binding], embed_position: Optional[Part] = None, streams: Optional[int] = None):
         """``embed_position``: a position encoding that acts on the residual stream right after the
         embedding (absolute or learned positions): a part with ``add_to(x, positions) -> x`` for the
         float32 stream x [T, width] and int32 positions [T] (-1: a padding row).  Rotary encodings are
-        not given here: they belong to the mixer that rotates with them."""
+        not given here: they belong to the mixer that rotates with them.
+        ``streams``: the number of residual streams per token (``parts/hyper.py``; the blocks are then ``HyperBlock``s);
+        None: one."""
         self.config = config
+        self.streams = streams
         self.embed_position = embed_position
         self.embed, self.blocks, self.order = embed, list(blocks), list(order)
         self.final_norm, self.head, self.bindings = final_norm, head, bindings
@@ -61,15 +66,20 @@ class DecoderModel:
                 continue
             if call.cache is None:
                 raise ConfigError(f"block {call.block} needs a cache entry")
-            if call.cache in entries and entries[call.cache] != spec:
-                raise ConfigError(f"cache entry {call.cache} is shared by mixers with different needs")
-            entries[call.cache] = spec
-            if call.store:
-                if call.cache in filled:
-                    raise ConfigError(f"cache entry {call.cache} is filled by two calls of the order")
-                filled.add(call.cache)
-            elif call.cache not in filled:
-                raise ConfigError(f"cache entry {call.cache} is read before any call fills it")
+            specs = tuple(spec) if isinstance(spec, (tuple, list)) else (spec,)
+            ids = tuple(call.cache) if isinstance(call.cache, (tuple, list)) else (call.cache,)
+            if len(specs) != len(ids):
+                raise ConfigError(f"block {call.block} has {len(specs)} cache needs but the order gives it {len(ids)} entries")
+            for one, eid in zip(specs, ids):
+                if eid in entries and entries[eid] != one:
+                    raise ConfigError(f"cache entry {eid} is shared by mixers with different needs")
+                entries[eid] = one
+                if call.store:
+                    if eid in filled:
+                        raise ConfigError(f"cache entry {eid} is filled by two calls of the order")
+                    filled.add(eid)
+                elif eid not in filled:
+                    raise ConfigError(f"cache entry {eid} is read before any call fills it")
         if sorted(entries) != list(range(len(entries))):
             raise ConfigError("cache entries must be numbered 0..n-1 without gaps")
         return [entries[i] for i in range(len(entries))]
@@ -86,6 +96,13 @@ class DecoderModel:
         for p in self.all_parts():
             p.materialize(self.device, dtype)
 
+    @staticmethod
+    def _view(views: Sequence[CacheView], eid: int, store: bool) -> CacheView:
+        view = views[eid]
+        if view.store != store:
+            view = CacheView(**{**view.__dict__, "store": store})
+        return view
+
     def forward(self, batch, views: Sequence[CacheView]) -> torch.Tensor:
         """Runs the batch's tokens through every call of the order; returns float32 logits
         [len(batch.logit_rows), vocab] - or None when ``batch.greedy_out`` was given and the head wrote the
@@ -93,18 +110,20 @@ class DecoderModel:
         x = self.embed.forward(batch.token_ids, batch.feedback)
         if self.embed_position is not None:
             x = self.embed_position.add_to(x, batch.positions)
+        if self.streams:
+            x = ops.hyper_expand(x, self.streams)
         pending = None
         for call in self.order:
             view = None
-            if call.cache is not None:
-                view = views[call.cache]
-                if view.store != call.store:
-                    view = CacheView(**{**view.__dict__, "store": call.store})
+            if isinstance(call.cache, (tuple, list)):
+                view = tuple(self._view(views, eid, call.store) for eid in call.cache)
+            elif call.cache is not None:
+                view = self._view(views, call.cache, call.store)
             x, pending = self.blocks[call.block].forward(x, pending, batch, view)
         if batch.num_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=x.device)
         greedy = getattr(batch, "greedy_out", None) if hasattr(self.head, "greedy") else None
-        if pending is None and hasattr(self.head, "can_fuse_norm") \
+        if pending is None and x.dim() == 2 and hasattr(self.head, "can_fuse_norm") \
                 and self.head.can_fuse_norm(x, self.final_norm, batch.num_logit_rows):
             if greedy is not None and self.head.greedy(x, self.final_norm, batch.logit_rows, batch.num_logit_rows, greedy):
                 return None

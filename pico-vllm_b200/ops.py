@@ -53,7 +53,7 @@ def library():
         "pico_swiglu": [vp, vp, i32, i32, i32, vp],
         "pico_rope_store": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
         "pico_paged_attention_generic": [vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
-                                         i32, i32, f32, i32, f32, i32, vp],
+                                         i32, i32, f32, i32, f32, i32, vp, i32, vp, vp],
         "pico_paged_prefill_mma": [vp, i32, vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp],
         "pico_paged_decode_mma": [vp, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
                                   f32, i32, f32, vp],
@@ -79,13 +79,13 @@ def library():
         "pico_scale_softcap": [vp, i32, i32, i32, f32, f32, vp],
         "pico_latent_norm_store": [vp, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, vp, f32, i32, i32, vp],
         "pico_head_scale": [vp, vp, i32, i32, i32, i32, vp],
-        "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, f32, vp],
         "pico_moe_group": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
         "pico_moe_tile_rows": [i32, i32, i32, i32, i32],
         "pico_moe_gather": [vp, vp, i32, i32, i32, vp, vp],
-        "pico_moe_combine_placed": [vp, vp, vp, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_combine_placed": [vp, vp, vp, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp],
         "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, i32, i32, vp],
-        "pico_moe_combine": [vp, vp, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_combine": [vp, vp, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp],
         "pico_moe_scaled_act": [vp, vp, vp, i32, i32, i32, vp, i32, vp],
         "pico_qk_norm_rope_store": [vp, i32, vp, vp, vp, f32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                     i32, i32, vp],
@@ -93,6 +93,20 @@ def library():
         "pico_decay_linear_attention": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp,
                                         vp, i32, i32, vp],
         "pico_gated_rms_norm": [vp, vp, vp, i32, f32, vp, i32, i32, i32, vp],
+        "pico_hyper_step": [vp, vp, vp, vp, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, vp],
+        "pico_hyper_expand": [vp, vp, i32, i32, i32, vp],
+        "pico_scale_add_rows": [vp, f32, vp, vp, i32, i32, i32, vp],
+        "pico_gated_linear_attention": [vp, i32, vp, i32, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
+                                        i32, i32, i32, vp, vp, vp],
+        "pico_scaled_sum": [vp, f32, vp, f32, vp, i64, i32, vp],
+        "pico_mlstm_prepare": [vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32,
+                               i32, i32, i32, i32, vp],
+        "pico_hgrn2_prepare": [vp, i32, i32, i32, i32, vp, vp, vp, i32, i32, i32, i32, vp],
+        "pico_causal_conv_silu": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+        "pico_mamba2_prepare": [vp, i32, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp],
+        "pico_group_rms_norm": [vp, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, vp],
+        "pico_whole_norm_store": [vp, i32, i32, i32, i32, vp, vp, f32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
+                                  i32, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -240,9 +254,13 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     tok_seg: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                     n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
                     scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
-                    softcap: Optional[float] = None) -> torch.Tensor:
+                    softcap: Optional[float] = None, slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of every token of the batch over its request's cache pages.
     ``softcap`` c: the scaled score s becomes c * tanh(s / c) before the softmax.
+    ``slopes`` float32 [n_heads]: slopes[h] * (query position - key position) is taken off head h's scores.
+    ``chunk`` C: the token at position p sees only keys from floor(p / C) * C on (positions count from the request's start).
+    ``sinks`` float32 [n_heads]: head h's softmax has one more term exp(sinks[h]) in its denominator and no value for it.
 
     q: [T, >= n_heads*head_dim] rows (the qkv buffer, queries first); out [T, n_heads*head_dim];
     tok_seg int32 [T]: row of block_table for each token; positions int32 [T]; block_table int32
@@ -267,6 +285,10 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     for t in (tok_seg, positions, block_table):
         if t.dtype != torch.int32:
             raise KernelError("paged_attention: index tensors must be int32")
+    _cuda(slopes, sinks)
+    for t in (slopes, sinks):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (n_heads,)):
+            raise KernelError("paged_attention: slopes and sinks must be float32 [n_heads]")
     part_o = part_ml = None
     if n_splits > 1:
         need = attention_scratch_floats(T, n_heads, head_dim, n_splits)
@@ -277,7 +299,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     _check(library().pico_paged_attention_generic(
         _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), part_o, part_ml, _ptr(tok_seg),
         _ptr(positions), _ptr(block_table), block_table.stride(0), T, n_heads, n_kv_heads, head_dim, page_size,
-        int(window) if window else 0, float(scale), n_splits, float(softcap) if softcap else 0.0, _dtype_code(q), _stream()),
+        int(window) if window else 0, float(scale), n_splits, float(softcap) if softcap else 0.0, _dtype_code(q),
+        _ptr(slopes), int(chunk) if chunk else 0, _ptr(sinks), _stream()),
         f"paged_attention (head_dim {head_dim})")
     _count(2 if n_splits > 1 else 1)
     return out
@@ -838,14 +861,16 @@ def head_scale(o: torch.Tensor, gate: torch.Tensor, heads: int) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------
 # Routed experts.
-MOE_SCORE_SOFTMAX_CHOSEN, MOE_SCORE_SIGMOID = 0, 1
+MOE_SCORE_SOFTMAX_CHOSEN, MOE_SCORE_SIGMOID, MOE_SCORE_SOFTMAX_ALL = 0, 1, 2
 MOE_ACT_SILU, MOE_ACT_RELU2 = 0, 1
 
 
 def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optional[torch.Tensor], top: int,
-              scoring: int = MOE_SCORE_SOFTMAX_CHOSEN):
+              scoring: int = MOE_SCORE_SOFTMAX_CHOSEN, choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0):
     """Router logits z = h W^T + b in float32, the ``top`` largest per token and the softmax over those alone
-    (``scoring`` MOE_SCORE_SIGMOID: each chosen expert's weight is sigmoid(z) of its own logit, not renormalised).
+    (``scoring`` MOE_SCORE_SIGMOID: each chosen expert's weight is sigmoid(z) of its own logit, not renormalised;
+    MOE_SCORE_SOFTMAX_ALL: an expert's score is its share of the softmax over all E logits, the ``top`` largest of score +
+    ``choice_bias`` (float32 [E]) are chosen, and the weight is the score itself times ``weight_scale``, not renormalised).
     h [T, D]; router_weight float32 [E, D]; router_bias float32 [E] or None.  Returns (idx int32 [T, top],
     weights float32 [T, top])."""
     _cuda(h, router_weight, router_bias)
@@ -856,17 +881,20 @@ def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optiona
         raise KernelError("moe_route: h must be contiguous [T, D] and the router weight float32 [E, D]")
     if router_bias is not None and (router_bias.dtype != torch.float32 or router_bias.shape != (E,)):
         raise KernelError("moe_route: the router bias must be float32 [E]")
+    if choice_bias is not None and (choice_bias.dtype != torch.float32 or choice_bias.shape != (E,) or not choice_bias.is_cuda):
+        raise KernelError("moe_route: the choice bias must be float32 [E]")
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     wgt = torch.empty((T, top), dtype=torch.float32, device=h.device)
     _check(library().pico_moe_route(_ptr(h), _ptr(router_weight), _ptr(router_bias), T, D, E, top, int(scoring), _ptr(idx), _ptr(wgt),
-                                    _dtype_code(h), _stream()), f"moe_route ({E} experts, top {top})")
+                                    _dtype_code(h), _ptr(choice_bias), float(weight_scale), _stream()),
+           f"moe_route ({E} experts, top {top})")
     _count()
     return idx, wgt
 
 
 def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_weight: torch.Tensor,
                 down_weight: torch.Tensor, gated: bool = True, act: int = MOE_ACT_SILU, weight_on_input: bool = False,
-                base: Optional[torch.Tensor] = None) -> torch.Tensor:
+                base: Optional[torch.Tensor] = None, identity: int = 0) -> torch.Tensor:
     """The routed experts' sum.  With e = idx[t, j]:
 
     gated, weight on the output (the default):  sum_j wgt[t, j] * down[e] (silu(gate[e] h_t) * (up[e] h_t)),
@@ -877,7 +905,8 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
 
     The (token, j) entries are listed per expert on the device, the two products run as grouped products over those
     lists, and the sum is taken in float32; ``base`` [T, D] (a shared expert's output) is added in the same kernel.
-    down_weight [E, D, ff]; all in h's type.  Returns [T, D] in h's type."""
+    down_weight [E, D, ff]; all in h's type.  ``identity`` n: idx may also name E .. E + n - 1, experts without tensors whose
+    output is their input (wgt[t, j] * h_t; weight on the output only).  Returns [T, D] in h's type."""
     _cuda(h, idx, wgt, gate_up_weight, down_weight, base)
     T, D = h.shape
     top = idx.shape[1]
@@ -895,15 +924,21 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
         raise KernelError("moe_experts: gated experts are built with silu and the weight on the output only")
     if base is not None and (base.shape != (T, D) or base.dtype != h.dtype or not base.is_contiguous()):
         raise KernelError("moe_experts: base must be contiguous [T, D] in h's type")
+    if identity and (weight_on_input or identity < 0):
+        raise KernelError("moe_experts: experts that pass their input on are built with the weight on the output only")
     n = T * top
     lib, code, st = library(), _dtype_code(h), _stream()
     grouped = moe_library_takes(h, n, D, ff)
-    meta = torch.empty(2 * (E + 1) + 2 * n, dtype=torch.int32, device=h.device)
-    offsets, tile_start = meta[:E + 1], meta[E + 1:2 * (E + 1)]
-    perm, place = meta[2 * (E + 1):2 * (E + 1) + n], meta[2 * (E + 1) + n:]
+    # entries are listed for the E real experts and, after them, for the ones that pass their input on: the products
+    # below see the first E lists only (offsets[E] and tile_start[E] end the real entries), the sum reads h for the rest
+    Et = E + identity
+    meta = torch.empty(2 * (Et + 1) + 2 * n, dtype=torch.int32, device=h.device)
+    offsets, tile_start = meta[:Et + 1], meta[Et + 1:2 * (Et + 1)]
+    perm, place = meta[2 * (Et + 1):2 * (Et + 1) + n], meta[2 * (Et + 1) + n:]
     bm = lib.pico_moe_tile_rows(n, E, code, D, ff)      # rows per tile of this package's grouped kernels
-    _check(lib.pico_moe_group(_ptr(idx), n, E, bm, _ptr(offsets), _ptr(tile_start), _ptr(perm),
+    _check(lib.pico_moe_group(_ptr(idx), n, Et, bm, _ptr(offsets), _ptr(tile_start), _ptr(perm),
                               _ptr(place) if grouped else None, st), "moe_group")
+    eidx, hsrc = (idx, h) if identity else (None, None)
     y = torch.empty((T, D), dtype=h.dtype, device=h.device)
     in_w = wgt if (not gated and weight_on_input) else None         # the weight inside the activation ...
     out_w = None if (not gated and weight_on_input) else wgt        # ... or on the expert's output
@@ -913,7 +948,7 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
         try:
             xs = torch.empty((n, D), dtype=h.dtype, device=h.device)
             _check(lib.pico_moe_gather(_ptr(h), _ptr(perm), n, top, D * h.element_size(), _ptr(xs), st), "moe_gather")
-            ends = offsets[1:]
+            ends = offsets[1:E + 1]
             gu = torch._grouped_mm(xs, gate_up_weight.transpose(1, 2), offs=ends)
             if gated:
                 a = torch.empty((n, ff), dtype=h.dtype, device=h.device)
@@ -923,8 +958,8 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
                 _check(lib.pico_moe_scaled_act(_ptr(gu), _ptr(perm), _ptr(in_w), n, ff, int(act), _ptr(a), code, st),
                        "moe_scaled_act")
             ys = torch._grouped_mm(a, down_weight.transpose(1, 2), offs=ends)
-            _check(lib.pico_moe_combine_placed(_ptr(ys), _ptr(place), _ptr(out_w), T, top, D, _ptr(y), _ptr(base), code, st),
-                   "moe_combine_placed")
+            _check(lib.pico_moe_combine_placed(_ptr(ys), _ptr(place), _ptr(out_w), T, top, D, _ptr(y), _ptr(base), code, _ptr(eidx), E,
+                                               _ptr(hsrc), st), "moe_combine_placed")
             _count(3)
             return y
         except (RuntimeError, NotImplementedError):
@@ -936,7 +971,8 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
     out2 = torch.empty((n, D), dtype=torch.float32, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(a), _ptr(down_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, D, ff,
                              1, bm, None, _ptr(out2), None, 0, code, st), "moe_gemm (down)")
-    _check(lib.pico_moe_combine(_ptr(out2), _ptr(out_w), T, top, D, _ptr(y), _ptr(base), code, st), "moe_combine")
+    _check(lib.pico_moe_combine(_ptr(out2), _ptr(out_w), T, top, D, _ptr(y), _ptr(base), code, _ptr(eidx), E, _ptr(hsrc), st),
+           "moe_combine")
     _count(4)
     return y
 
@@ -1078,3 +1114,277 @@ def moe_library_takes(h: torch.Tensor, n: int, D: int, ff: int) -> bool:
     that are multiples of 16 bytes) instead of this package's grouped kernels."""
     return (h.dtype == torch.bfloat16 and n >= MOE_LIBRARY_MIN_ROWS and D % 8 == 0 and ff % 8 == 0
             and hasattr(torch, "_grouped_mm"))
+
+
+# ------------------------------------------------------------------------------------------ several residual streams
+def hyper_expand(x: torch.Tensor, streams: int) -> torch.Tensor:
+    """[T, D] float32 -> [T, streams, D]: every stream starts as a copy of the embedding stage's output."""
+    _cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous() or streams < 1:
+        raise KernelError("hyper_expand: x must be contiguous float32 [T, D]")
+    T, D = x.shape
+    out = torch.empty((T, streams, D), dtype=torch.float32, device=x.device)
+    _check(library().pico_hyper_expand(_ptr(x), _ptr(out), T, streams, D, _stream()), "hyper_expand")
+    _count()
+    return out
+
+
+def hyper_step(x: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor], out_w: Optional[torch.Tensor],
+               in_w: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One pass over a token's residual streams x float32 [T, S, D]: first the write of the sublayer whose output ``y``
+    [T, D] is still pending,  x_t <- sum_s mix[s, t] x_s + out_w[t] y  (all t from the old streams; skipped when y is
+    None), then the read of the next one,  u = sum_s in_w[s] x_s  (``in_w`` None: the plain sum), RMS-normed with the
+    weight ``norm_w`` float32 [D] and returned [T, D] in ``out_dtype``.  With ``rows`` (int32) only those tokens are read
+    and x is not written."""
+    _cuda(x, y, mix, out_w, in_w, norm_w, rows)
+    if x.dtype != torch.float32 or x.dim() != 3 or not x.is_contiguous():
+        raise KernelError("hyper_step: the streams must be contiguous float32 [T, S, D]")
+    T, S, D = x.shape
+    if y is not None and (y.shape != (T, D) or not y.is_contiguous() or y.dtype != out_dtype or mix is None or out_w is None):
+        raise KernelError("hyper_step: the pending output must be contiguous [T, D] in the activation type, with its mix and out weights")
+    for t, shape in ((mix, (S, S)), (out_w, (S,)), (in_w, (S,)), (norm_w, (D,))):
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous()):
+            raise KernelError(f"hyper_step: a weight must be contiguous float32 {list(shape)}")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("hyper_step: rows must be int32")
+    R = T if rows is None else rows.shape[0]
+    h = torch.empty((R, D), dtype=out_dtype, device=x.device)
+    _check(library().pico_hyper_step(_ptr(x), _ptr(y), _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(norm_w), float(eps), _ptr(h),
+                                     _ptr(rows), None, R, S, D, _dtype_code(h), _stream()), f"hyper_step ({S} streams)")
+    _count()
+    return h
+
+
+def scale_add_rows(x: torch.Tensor, scale: float, table: Optional[torch.Tensor], positions: Optional[torch.Tensor]) -> torch.Tensor:
+    """x[t] <- x[t] * scale + table[positions[t]] in place on the float32 stream x [T, D] (a negative position gets no
+    row; ``table`` None: the scale alone)."""
+    _cuda(x, table, positions)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("scale_add_rows: x must be contiguous float32 [T, D]")
+    T, D = x.shape
+    if table is not None and (table.dim() != 2 or table.shape[1] != D or not table.is_contiguous() or positions is None
+                              or positions.dtype != torch.int32 or positions.shape[0] != T):
+        raise KernelError("scale_add_rows: the table must be contiguous [rows, D] and positions int32 [T]")
+    _check(library().pico_scale_add_rows(_ptr(x), float(scale), _ptr(table), _ptr(positions), T, D,
+                                         _dtype_code(table) if table is not None else _F32, _stream()), "scale_add_rows")
+    _count()
+    return x
+
+
+def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float) -> torch.Tensor:
+    """sa * a + sb * b in float32, returned in the tensors' own type."""
+    _cuda(a, b)
+    if a.shape != b.shape or a.dtype != b.dtype or not a.is_contiguous() or not b.is_contiguous():
+        raise KernelError("scaled_sum: two contiguous tensors of one shape and type")
+    out = torch.empty_like(a)
+    _check(library().pico_scaled_sum(_ptr(a), float(sa), _ptr(b), float(sb), _ptr(out), a.numel(), _dtype_code(a), _stream()),
+           "scaled_sum")
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------------------------------ recurrences with gates per token
+def _f32_rows(t: torch.Tensor, what: str) -> None:
+    if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what} must be float32 rows with contiguous columns")
+
+
+def gated_linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor, per_row: bool,
+                           state: torch.Tensor, seg_slots: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor,
+                           heads: int, qk_rep: int, dim: int, vdim: int, max_q_len: int = 1,
+                           chunk: Optional[int] = None) -> torch.Tensor:
+    """Per head h:  S <- diag(a_t) S + k_t v_t^T,  o_t = S^T q_t  (S [dim, vdim]), token by token in the order of each
+    segment, from and into ``state`` float32 [slots, heads, vdim, dim] (S transposed; row ``seg_slots[s]``).  q, k, v and
+    gate are float32 rows (column slices are fine): head h reads q and k at (h // qk_rep) * dim (``qk_rep`` heads share a
+    query and key), v at h * vdim, and its gate a_t at h (one number a head, ``per_row`` False) or at h * dim .. (one a
+    row of S).  A segment whose first position is negative is padding.  Returns o float32 [T, heads * vdim].
+    Long segments (``max_q_len`` from LINEAR_CHUNK_MIN_TOKENS on, or ``chunk`` > 0) run as chunks side by side: local
+    states and gate products, a scan, then the outputs."""
+    _cuda(q, k, v, gate, state, seg_slots, cu_q, positions)
+    for t, what in ((q, "q"), (k, "k"), (v, "v"), (gate, "gate")):
+        _f32_rows(t, f"gated_linear_attention: {what}")
+    T, S = q.shape[0], seg_slots.shape[0]
+    groups = heads // max(qk_rep, 1)
+    if qk_rep < 1 or heads % qk_rep or q.shape[1] < groups * dim or k.shape[1] < groups * dim or v.shape[1] < heads * vdim \
+            or gate.shape[1] < heads * (dim if per_row else 1) or not (k.shape[0] == v.shape[0] == gate.shape[0] == T):
+        raise KernelError("gated_linear_attention: a row is narrower than its heads")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, vdim, dim):
+        raise KernelError("gated_linear_attention: state must be contiguous float32 [slots, heads, vdim, dim]")
+    for t in (seg_slots, cu_q, positions):
+        if t.dtype != torch.int32:
+            raise KernelError("gated_linear_attention: index tensors must be int32")
+    if cu_q.shape[0] != S + 1 or positions.shape[0] != T:
+        raise KernelError("gated_linear_attention: cu_q must have one more entry than seg_slots, positions one per token")
+    out = torch.empty((T, heads * vdim), dtype=torch.float32, device=q.device)
+    if chunk is None:
+        chunk = LINEAR_CHUNK if max_q_len >= LINEAR_CHUNK_MIN_TOKENS else 0
+    chunk_state = chunk_gate = None
+    if chunk > 0:
+        n = T // chunk + S
+        chunk_state = torch.empty(n * heads * vdim * dim, dtype=torch.float32, device=q.device)
+        chunk_gate = torch.empty(n * heads * dim, dtype=torch.float32, device=q.device)
+    _check(library().pico_gated_linear_attention(
+        _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(gate), gate.stride(0), 2 if per_row else 1,
+        _ptr(state), _ptr(seg_slots), _ptr(cu_q), _ptr(positions), _ptr(out), out.stride(0), S, heads, qk_rep, dim, vdim,
+        int(chunk), int(max(max_q_len, 1)), _ptr(chunk_state), _ptr(chunk_gate), _stream()),
+        f"gated_linear_attention (dim {dim})")
+    _count(3 if chunk > 0 else 1)
+    return out
+
+
+def mlstm_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, i_off: int, f_off: int,
+                  i_bias: Optional[torch.Tensor], f_bias: Optional[torch.Tensor], cap: float, q_scale: float,
+                  m_state: torch.Tensor, seg_slots: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor,
+                  heads: int, dim: int, vdim: int):
+    """The gates of a matrix memory with exponential gating, kept finite by a running maximum m per head (``m_state``
+    float32 [slots, heads], carried on):  i = cap tanh((z_i + b_i) / cap),  f = logsigmoid(cap tanh((z_f + b_f) / cap)),
+    m_t = max(f + m_(t-1), i).  Returns (keep [T, heads] = exp(f + m_(t-1) - m_t), floor [T, heads] = exp(-m_t), prepared
+    float32 [T, q: heads*dim | k: heads*dim | v: heads*(vdim+1)] with q * q_scale, k * exp(i - m_t), and one more column of
+    ones after each head's values, whose row of the memory is the normaliser)."""
+    _cuda(proj, i_bias, f_bias, m_state, seg_slots, cu_q, positions)
+    T, S = proj.shape[0], seg_slots.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1 or max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim,
+                                                     i_off + heads, f_off + heads) > proj.shape[1]:
+        raise KernelError("mlstm_prepare: the projection row is narrower than its parts")
+    if m_state.dtype != torch.float32 or not m_state.is_contiguous() or tuple(m_state.shape[1:]) != (heads,):
+        raise KernelError("mlstm_prepare: the running maximum must be contiguous float32 [slots, heads]")
+    for t in (i_bias, f_bias):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (heads,)):
+            raise KernelError("mlstm_prepare: gate biases must be float32 [heads]")
+    dev = proj.device
+    gates = torch.empty((3, T, heads), dtype=torch.float32, device=dev)
+    prepared = torch.empty((T, 2 * heads * dim + heads * (vdim + 1)), dtype=torch.float32, device=dev)
+    _check(library().pico_mlstm_prepare(_ptr(proj), proj.stride(0), q_off, k_off, v_off, i_off, f_off, _ptr(i_bias), _ptr(f_bias),
+                                        float(cap), float(q_scale), _ptr(m_state), _ptr(seg_slots), _ptr(cu_q), _ptr(positions),
+                                        _ptr(gates[0]), _ptr(gates[1]), _ptr(gates[2]), _ptr(prepared), T, S, heads, dim, vdim,
+                                        _dtype_code(proj), _stream()), "mlstm_prepare")
+    _count(2)
+    return gates[0], gates[2], prepared
+
+
+def hgrn2_prepare(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: Optional[torch.Tensor],
+                  lower: Optional[torch.Tensor], nqk: int, nv: int) -> torch.Tensor:
+    """float32 [T, q: nqk | k: nqk | f: nqk | v: nv] with q = silu(z_q), f = lower + (1 - lower) sigmoid(z_f + b_f) and
+    k = 1 - f: a forget gate that also decides what is written."""
+    _cuda(proj, f_bias, lower)
+    T = proj.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1 or max(q_off + nqk, f_off + nqk, v_off + nv) > proj.shape[1]:
+        raise KernelError("hgrn2_prepare: the projection row is narrower than its parts")
+    for t in (f_bias, lower):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (nqk,)):
+            raise KernelError("hgrn2_prepare: the gate's bias and lower bound must be float32 [heads * dim]")
+    prepared = torch.empty((T, 3 * nqk + nv), dtype=torch.float32, device=proj.device)
+    _check(library().pico_hgrn2_prepare(_ptr(proj), proj.stride(0), q_off, f_off, v_off, _ptr(f_bias), _ptr(lower), _ptr(prepared),
+                                        T, nqk, nv, _dtype_code(proj), _stream()), "hgrn2_prepare")
+    _count()
+    return prepared
+
+
+def causal_conv_silu(proj: torch.Tensor, c_off: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                     conv_state: torch.Tensor, tok_seg: torch.Tensor, seg_slots: torch.Tensor, cu_q: torch.Tensor,
+                     positions: torch.Tensor) -> torch.Tensor:
+    """silu of a causal convolution per channel over the tokens of each segment: out[t, c] = silu(b[c] + sum_j w[c, j] *
+    in(t - (taps - 1) + j, c)), the last tap on the token itself.  The channels are columns c_off .. of ``proj``; inputs from
+    before the segment come from ``conv_state`` float32 [slots, taps - 1, C] (zero at a request's start), which afterwards
+    holds the segment's last taps - 1 inputs.  Returns float32 [T, C]."""
+    _cuda(proj, weight, bias, conv_state, tok_seg, seg_slots, cu_q, positions)
+    T, S = proj.shape[0], seg_slots.shape[0]
+    C, taps = weight.shape
+    if proj.dim() != 2 or proj.stride(1) != 1 or c_off + C > proj.shape[1]:
+        raise KernelError("causal_conv_silu: the projection row is narrower than the channels")
+    if weight.dtype != torch.float32 or not weight.is_contiguous() or (bias is not None and (bias.dtype != torch.float32 or bias.shape != (C,))):
+        raise KernelError("causal_conv_silu: weight float32 [C, taps], bias float32 [C]")
+    if conv_state.dtype != torch.float32 or not conv_state.is_contiguous() or tuple(conv_state.shape[1:]) != (taps - 1, C):
+        raise KernelError("causal_conv_silu: the state must be contiguous float32 [slots, taps - 1, C]")
+    out = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    _check(library().pico_causal_conv_silu(_ptr(proj), proj.stride(0), c_off, _ptr(weight), _ptr(bias), _ptr(conv_state),
+                                           _ptr(tok_seg), _ptr(seg_slots), _ptr(cu_q), _ptr(positions), _ptr(out), T, S, C, taps,
+                                           _dtype_code(proj), _stream()), f"causal_conv_silu ({taps} taps)")
+    _count(2 if taps > 1 else 1)
+    return out
+
+
+def mamba2_prepare(proj: torch.Tensor, dt_off: int, dt_bias: Optional[torch.Tensor], a_log: torch.Tensor, x: torch.Tensor,
+                   heads: int, vdim: int):
+    """Step size and decay of a state-space layer: dt = softplus(z_dt + dt_bias) (no clamp), keep [T, heads] =
+    exp(-exp(a_log) dt), vdt [T, heads * vdim] = dt * x.  x: float32 rows (a column slice is fine)."""
+    _cuda(proj, dt_bias, a_log, x)
+    T = proj.shape[0]
+    _f32_rows(x, "mamba2_prepare: x")
+    if proj.dim() != 2 or proj.stride(1) != 1 or dt_off + heads > proj.shape[1] or x.shape[1] < heads * vdim or x.shape[0] != T:
+        raise KernelError("mamba2_prepare: a row is narrower than its heads")
+    for t in (dt_bias, a_log):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (heads,)):
+            raise KernelError("mamba2_prepare: dt_bias and a_log must be float32 [heads]")
+    keep = torch.empty((T, heads), dtype=torch.float32, device=proj.device)
+    vdt = torch.empty((T, heads * vdim), dtype=torch.float32, device=proj.device)
+    _check(library().pico_mamba2_prepare(_ptr(proj), proj.stride(0), dt_off, _ptr(dt_bias), _ptr(a_log), _ptr(x), x.stride(0),
+                                         _ptr(keep), _ptr(vdt), T, heads, vdim, _dtype_code(proj), _stream()), "mamba2_prepare")
+    _count()
+    return keep, vdt
+
+
+def group_rms_norm(x: torch.Tensor, groups: int, n: int, group_stride: int, weight: Optional[torch.Tensor], eps: float,
+                   out_dtype: torch.dtype, den_floor: Optional[torch.Tensor] = None, skip: Optional[torch.Tensor] = None,
+                   skip_w: Optional[torch.Tensor] = None, skip_head: int = 1, pre_gate: Optional[torch.Tensor] = None,
+                   post_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The norm that finishes a recurrent mixer, a root mean square per group of ``n`` columns (group g starts at column
+    g * group_stride of x, float32 rows).  For column j of group g, col = g * n + j, in this order:
+      ``den_floor`` [T, groups]: val /= max(|x[t, g * group_stride + n]|, den_floor[t, g]) + 1e-6 (a normaliser that rides
+      as column n of its group);  ``skip`` (float32 rows) with ``skip_w``: val += skip_w[col // skip_head] * skip[t, col];
+      ``pre_gate``: val *= silu(pre_gate[t, col]);  y = val / sqrt(mean_j val^2 + eps) * weight[col];
+      ``post_gate``: y *= sigmoid(post_gate[t, col]).  Gates are in ``out_dtype`` (column slices are fine).
+    Returns [T, groups * n] in ``out_dtype``."""
+    _cuda(x, weight, den_floor, skip, skip_w, pre_gate, post_gate)
+    _f32_rows(x, "group_rms_norm: x")
+    T, N = x.shape[0], groups * n
+    if x.shape[1] < (groups - 1) * group_stride + n + (1 if den_floor is not None else 0):
+        raise KernelError("group_rms_norm: x is narrower than its groups")
+    if weight is not None and (weight.dtype != torch.float32 or weight.shape != (N,)):
+        raise KernelError("group_rms_norm: weight must be float32 [groups * n]")
+    if den_floor is not None and (den_floor.dtype != torch.float32 or den_floor.shape != (T, groups) or not den_floor.is_contiguous()):
+        raise KernelError("group_rms_norm: den_floor must be contiguous float32 [T, groups]")
+    if skip is not None:
+        _f32_rows(skip, "group_rms_norm: skip")
+        if skip.shape[1] < N or skip_w is None or skip_w.dtype != torch.float32 or skip_w.numel() * skip_head < N:
+            raise KernelError("group_rms_norm: skip needs float32 weights, one per skip_head columns")
+    for g in (pre_gate, post_gate):
+        if g is not None and (g.dtype != out_dtype or g.dim() != 2 or g.stride(1) != 1 or g.shape[0] != T or g.shape[1] < N):
+            raise KernelError("group_rms_norm: gates must be rows in the output type")
+    y = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    _check(library().pico_group_rms_norm(_ptr(x), x.stride(0), group_stride, groups, n, _ptr(weight), float(eps), _ptr(den_floor),
+                                         _ptr(skip), skip.stride(0) if skip is not None else 0, _ptr(skip_w), int(skip_head),
+                                         _ptr(pre_gate), pre_gate.stride(0) if pre_gate is not None else 0, _ptr(post_gate),
+                                         post_gate.stride(0) if post_gate is not None else 0, _ptr(y), T, _dtype_code(y), _stream()),
+           "group_rms_norm")
+    _count()
+    return y
+
+
+def whole_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w: Optional[torch.Tensor],
+                     k_w: Optional[torch.Tensor], eps: float, v_norm: bool, slots: Optional[torch.Tensor],
+                     k_pages: torch.Tensor, v_pages: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, row: int,
+                     page_size: int) -> torch.Tensor:
+    """Queries and keys RMS-normed over their whole projection (all heads of a token at once; weights ``q_w`` float32
+    [heads * dim], ``k_w`` [kv_heads * dim]; None: no norm), values divided by their root mean square per head (``v_norm``),
+    keys and values written to the token's place in the pages [pages, kv_heads, page_size, row] (``slots`` int32; -1 or None:
+    not stored).  Heads are padded with zeros to ``row`` elements.  Returns the queries [T, heads * row]."""
+    _cuda(proj, q_w, k_w, slots, k_pages, v_pages)
+    T = proj.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1 or max(q_off + heads * dim, k_off + kv_heads * dim, v_off + kv_heads * vdim) > proj.shape[1]:
+        raise KernelError("whole_norm_store: the projection row is narrower than its parts")
+    for t, n in ((q_w, heads * dim), (k_w, kv_heads * dim)):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (n,)):
+            raise KernelError("whole_norm_store: norm weights must be float32 over the whole projection")
+    for t in (k_pages, v_pages):
+        if t.dtype != proj.dtype or t.dim() != 4 or tuple(t.shape[1:]) != (kv_heads, page_size, row) or not t.is_contiguous():
+            raise KernelError("whole_norm_store: pages must be contiguous [pages, kv_heads, page_size, row] in the activation type")
+    if slots is not None and (slots.dtype != torch.int32 or slots.shape[0] != T):
+        raise KernelError("whole_norm_store: slots must be int32 [T]")
+    q_out = torch.empty((T, heads * row), dtype=proj.dtype, device=proj.device)
+    _check(library().pico_whole_norm_store(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(q_w), _ptr(k_w), float(eps),
+                                           1 if v_norm else 0, _ptr(slots), _ptr(k_pages), _ptr(v_pages), _ptr(q_out), T, heads,
+                                           kv_heads, dim, vdim, row, page_size, _dtype_code(proj), _stream()), "whole_norm_store")
+    _count()
+    return q_out

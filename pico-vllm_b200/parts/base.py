@@ -38,7 +38,8 @@ class Param:
     attr: str
     pieces: Tuple[Piece, ...]
     kind: str = "matrix"     # "matrix": model dtype unless stored in 32-bit; "vector": float32
-    init: str = "normal"     # random-weights rule: "normal" N(0, std) or "one_plus_normal"
+    init: str = "normal"     # random-weights rule: "normal" N(0, std), "one_plus_normal", "identity" (a square matrix
+                             # around the identity) or "const:<number>" (around that number)
 
     @property
     def shape(self) -> Tuple[int, ...]:

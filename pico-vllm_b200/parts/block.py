@@ -14,17 +14,23 @@ from .base import CacheView, Part
 
 
 class PreNormBlock:
-    def __init__(self, norm1: Part, mixer: Part, norm2: Part, feed_forward: Part):
+    def __init__(self, norm1: Part, mixer: Part, norm2: Optional[Part] = None, feed_forward: Optional[Part] = None):
+        """``feed_forward`` (with ``norm2``) may be None: the layer is then its mixer alone."""
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
 
     def parts(self):
-        return {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "feed_forward": self.feed_forward}
+        p = {"norm1": self.norm1, "mixer": self.mixer}
+        if self.feed_forward is not None:
+            p.update(norm2=self.norm2, feed_forward=self.feed_forward)
+        return p
 
     def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], batch,
                 cache: CacheView) -> Tuple[torch.Tensor, torch.Tensor]:
         """x: float32 residual stream [T, width]; pending: output of the previous part that is
         still to be added to x (or None).  Returns (x, pending) in the same sense."""
         a = self._run(self.norm1, self.mixer, x, pending, batch, cache)
+        if self.feed_forward is None:
+            return x, a
         return x, self._run(self.norm2, self.feed_forward, x, a, batch)
 
     @staticmethod

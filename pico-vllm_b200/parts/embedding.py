@@ -29,6 +29,21 @@ class TokenEmbedding(Part):
         return ops.embedding(ids, self.weight, out, feedback)
 
 
+class LearnedPositions(Part):
+    """A learned vector per position, added to the residual stream right after the embedding:  x <- x * input_scale +
+    table[position]  (the scale acts on the token embedding only).  A request cannot grow beyond the table."""
+
+    def __init__(self, max_positions: int, width: int, input_scale: float = 1.0):
+        self.max_positions, self.width, self.input_scale = max_positions, width, float(input_scale)
+        self.weight = None
+
+    def params(self) -> List[Param]:
+        return [Param("weight", (Piece("weight", (self.max_positions, self.width)),))]
+
+    def add_to(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        return ops.scale_add_rows(x, self.input_scale, self.weight, positions)
+
+
 class OutputHead(Part):
     def __init__(self, vocab: int, width: int, tied_to: Optional[TokenEmbedding] = None, logit_scale: float = 1.0,
                  softcap: Optional[float] = None):

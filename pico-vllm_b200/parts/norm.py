@@ -67,11 +67,31 @@ class RMSNorm(Part):
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: float32 [T, width] residual stream, updated in place by ``x += delta`` unless
         ``rows`` picks rows (then x stays).  Returns norm(x) in the activation dtype."""
+        if x.dim() == 3:                # several residual streams [T, S, width]: what is read is their sum
+            from .hyper import streams_add_norm
+            return streams_add_norm(self, x, delta, None, rows)
         if isinstance(delta, NormedDelta):
             return _post_add_norm(self, ops.NORM_RMS, x, delta, rows)
         n = rows.shape[0] if rows is not None else x.shape[0]
         out = torch.empty((n, self.width), dtype=self.act_dtype, device=x.device)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
+
+
+@register("norm", "scalar_rmsnorm")
+class ScalarRMSNorm(RMSNorm):
+    """y = x * rsqrt(mean(x^2) + eps) * g with ONE learned number g for all coordinates.  The number is spread over a
+    vector when it is loaded, so the kernels see an ordinary RMS norm."""
+
+    def __init__(self, width: int, eps: float):
+        super().__init__(width, eps, one_plus=False)
+
+    def params(self) -> List[Param]:
+        return [Param("weight", (Piece("weight", ()),), kind="vector", init="one_plus_normal")]
+
+    def assign(self, attr: str, tensor: torch.Tensor) -> None:
+        if attr == "weight":
+            tensor = tensor.to(torch.float32).reshape(1).expand(self.width).contiguous()
+        setattr(self, attr, tensor)
 
 
 @register("norm", "centred_norm")

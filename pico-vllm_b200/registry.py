@@ -48,6 +48,9 @@ def _register_builtin() -> None:
     from .config.zikupel import ZikupelConfig
     from .models.zikupel import build_zikupel
     register_architecture("Zikupel", ZikupelConfig, build_zikupel)
+    from .config.zazilix import ZazilixConfig
+    from .models.zazilix import build_zazilix
+    register_architecture("Zazilix", ZazilixConfig, build_zazilix)
 
 
 _register_builtin()

@@ -1,5 +1,6 @@
 """Random-weights mode: writes a model folder (config.json, model.safetensors) from a
-configuration and a seed.  Matrices and biases ~ N(0, std), norm weights 1 + N(0, std), drawn
+configuration and a seed.  Matrices and biases ~ N(0, std), norm weights 1 + N(0, std) (a parameter's ``init`` may also ask
+for the identity or a given number plus that noise), drawn
 on the CPU in float32 and stored in ``dtype``.  Every tensor has a generator of its own, keyed
 by (seed, index of the tensor in the order of the model's bindings), so tensors can be drawn
 in parallel and still depend on nothing but the seed.  The reference has no such mode (it
@@ -32,6 +33,10 @@ def random_tensors(config, seed: int, std: float = 0.02, dtype: torch.dtype = to
         t = torch.from_numpy(rng.standard_normal(shape, dtype=np.float32)) * std
         if init == "one_plus_normal":
             t = t + 1.0
+        elif init == "identity":                  # a square matrix around the identity
+            t = t + torch.eye(shape[0], dtype=torch.float32)
+        elif init.startswith("const:"):           # around a given number
+            t = t + float(init[6:])
         return name, t.to(dtype)
 
     with ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as pool:
