@@ -76,7 +76,8 @@ def attention_scratch_floats(T, n_heads, head_dim, n_splits):
 
 
 def paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n_heads, n_kv_heads,
-                    head_dim, page_size, window, scale, n_splits=1, scratch=None, softcap=None):
+                    head_dim, page_size, window, scale, n_splits=1, scratch=None, softcap=None, slopes=None, chunk=None,
+                    sinks=None):
     T = q.shape[0]
     g = n_heads // n_kv_heads
     for t in range(T):
@@ -85,6 +86,8 @@ def paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n
             out[t] = 0
             continue
         lo = max(0, p + 1 - window) if window else 0
+        if chunk:
+            lo = max(lo, p // chunk * chunk)
         n = torch.arange(lo, p + 1)
         pages = block_table[int(tok_seg[t])].long()[n // page_size]
         k = k_pages[pages, :, n % page_size, :].float()    # [keys, kv_heads, hd]
@@ -94,7 +97,13 @@ def paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n
             s = (k[:, h // g, :] @ qt[h]) * scale
             if softcap:
                 s = softcap * torch.tanh(s / softcap)
-            pr = torch.softmax(s, dim=0)
+            if slopes is not None:
+                s = s - float(slopes[h]) * (p - n).float()
+            if sinks is not None:
+                e = torch.exp(s - float(sinks[h]))
+                pr = e / (1.0 + e.sum())
+            else:
+                pr = torch.softmax(s, dim=0)
             out[t, h * head_dim:(h + 1) * head_dim] = (pr @ v[:, h // g, :]).to(out.dtype)
     return out
 
@@ -271,10 +280,14 @@ def head_scale(o, gate, heads):
     return o
 
 
-def moe_route(h, router_weight, router_bias, top, scoring=0):
+def moe_route(h, router_weight, router_bias, top, scoring=0, choice_bias=None, weight_scale=1.0):
     z = h.float() @ router_weight.t()
     if router_bias is not None:
         z = z + router_bias
+    if scoring == 2:
+        score = torch.softmax(z, dim=-1)
+        idx = torch.topk(score + (choice_bias if choice_bias is not None else 0.0), top, dim=-1).indices
+        return idx.to(torch.int32), torch.gather(score, 1, idx) * weight_scale
     val, idx = torch.topk(z, top, dim=-1)
     return idx.to(torch.int32), (torch.sigmoid(val) if scoring == 1 else torch.softmax(val, dim=-1))
 
@@ -283,13 +296,16 @@ def _act(u, act):
     return torch.relu(u) ** 2 if act == 1 else u * torch.sigmoid(u)
 
 
-def moe_experts(h, idx, wgt, gate_up_weight, down_weight, gated=True, act=0, weight_on_input=False, base=None):
+def moe_experts(h, idx, wgt, gate_up_weight, down_weight, gated=True, act=0, weight_on_input=False, base=None, identity=0):
     ff = gate_up_weight.shape[1] // 2 if gated else gate_up_weight.shape[1]
     y = torch.zeros(h.shape, dtype=torch.float32) if base is None else base.float().clone()
     for t in range(h.shape[0]):
         for j in range(idx.shape[1]):
             e = int(idx[t, j])
-            if gated:
+            if e >= gate_up_weight.shape[0]:
+                assert e < gate_up_weight.shape[0] + identity
+                y[t] += wgt[t, j] * h[t].float()
+            elif gated:
                 gu = gate_up_weight[e].float() @ h[t].float()
                 g, u = gu[:ff], gu[ff:]
                 y[t] += wgt[t, j] * (down_weight[e].float() @ (g * torch.sigmoid(g) * u))
@@ -371,7 +387,159 @@ def gated_rms_norm(x, weight, gate_logits, eps, out_dtype):
     return y.to(out_dtype)
 
 
-NAMES = ["activation", "qk_norm_rope_store", "sigmoid_gate", "decay_linear_attention", "gated_rms_norm", "post_add_norm", "scale_softcap", "latent_norm_store", "head_linear", "head_scale", "moe_route", "moe_experts",
+# ------------------------------------------------------------------ several streams, recurrences with gates per token
+def hyper_expand(x, streams):
+    return x[:, None, :].repeat(1, streams, 1)
+
+
+def _rms_unit(u, eps):
+    return u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps)
+
+
+def hyper_step(x, y, mix, out_w, in_w, norm_w, eps, out_dtype, rows=None):
+    new = x if y is None else torch.einsum("sr,tsd->trd", mix, x) + out_w[None, :, None] * y.float()[:, None, :]
+    if rows is None:
+        x.copy_(new)
+    else:
+        new = new[rows.long()]
+    u = new.sum(1) if in_w is None else torch.einsum("s,tsd->td", in_w, new)
+    return (_rms_unit(u, eps) * norm_w).to(out_dtype)
+
+
+def scale_add_rows(x, scale, table, positions):
+    x.mul_(scale)
+    if table is not None:
+        live = positions >= 0
+        x[live] += table[positions[live].long()].float()
+    return x
+
+
+def scaled_sum(a, sa, b, sb):
+    return (sa * a.float() + sb * b.float()).to(a.dtype)
+
+
+def gated_linear_attention(q, k, v, gate, per_row, state, seg_slots, cu_q, positions, heads, qk_rep, dim, vdim, max_q_len=1,
+                           chunk=None):
+    T = q.shape[0]
+    out = torch.zeros(T, heads * vdim)
+    for s in range(seg_slots.shape[0]):
+        a0, a1 = int(cu_q[s]), int(cu_q[s + 1])
+        if a1 <= a0 or int(positions[a0]) < 0:
+            continue
+        for h in range(heads):
+            S = state[int(seg_slots[s]), h].T.clone()                       # [dim, vdim]
+            g0 = (h // qk_rep) * dim
+            for t in range(a0, a1):
+                a = gate[t, h * dim:(h + 1) * dim][:, None] if per_row else gate[t, h]
+                S = a * S + torch.outer(k[t, g0:g0 + dim], v[t, h * vdim:(h + 1) * vdim])
+                out[t, h * vdim:(h + 1) * vdim] = S.T @ q[t, g0:g0 + dim]
+            state[int(seg_slots[s]), h] = S.T
+    return out
+
+
+def mlstm_prepare(proj, q_off, k_off, v_off, i_off, f_off, i_bias, f_bias, cap, q_scale, m_state, seg_slots, cu_q, positions,
+                  heads, dim, vdim):
+    T, H = proj.shape[0], heads
+    p = proj.float()
+    gi = cap * torch.tanh((p[:, i_off:i_off + H] + (i_bias if i_bias is not None else 0.0)) / cap)
+    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((p[:, f_off:f_off + H] + (f_bias if f_bias is not None else 0.0)) / cap))
+    keep, put, floor = torch.ones(T, H), torch.zeros(T, H), torch.ones(T, H)
+    for s in range(seg_slots.shape[0]):
+        a0, a1 = int(cu_q[s]), int(cu_q[s + 1])
+        if a1 <= a0 or int(positions[a0]) < 0:
+            continue
+        m = m_state[int(seg_slots[s])].clone()
+        for t in range(a0, a1):
+            new = torch.maximum(gf[t] + m, gi[t])
+            keep[t], put[t], floor[t] = torch.exp(gf[t] + m - new), torch.exp(gi[t] - new), torch.exp(-new)
+            m = new
+        m_state[int(seg_slots[s])] = m
+    q = p[:, q_off:q_off + H * dim] * q_scale
+    k = (p[:, k_off:k_off + H * dim].view(T, H, dim) * put[:, :, None]).reshape(T, H * dim)
+    v = torch.cat([p[:, v_off:v_off + H * vdim].view(T, H, vdim), torch.ones(T, H, 1)], 2).reshape(T, H * (vdim + 1))
+    return keep, floor, torch.cat([q, k, v], 1)
+
+
+def hgrn2_prepare(proj, q_off, f_off, v_off, f_bias, lower, nqk, nv):
+    p = proj.float()
+    q = p[:, q_off:q_off + nqk]
+    lo = lower if lower is not None else 0.0
+    f = lo + (1.0 - lo) * torch.sigmoid(p[:, f_off:f_off + nqk] + (f_bias if f_bias is not None else 0.0))
+    return torch.cat([q * torch.sigmoid(q), 1.0 - f, f, p[:, v_off:v_off + nv]], 1)
+
+
+def causal_conv_silu(proj, c_off, weight, bias, conv_state, tok_seg, seg_slots, cu_q, positions):
+    C, taps = weight.shape
+    T = proj.shape[0]
+    out = torch.zeros(T, C)
+    for s in range(seg_slots.shape[0]):
+        a0, a1 = int(cu_q[s]), int(cu_q[s + 1])
+        if a1 <= a0 or int(positions[a0]) < 0:
+            continue
+        slot = int(seg_slots[s])
+        x = torch.cat([conv_state[slot], proj[a0:a1, c_off:c_off + C].float()])        # [taps - 1 + n, C]
+        for t in range(a1 - a0):
+            acc = (x[t:t + taps] * weight.t()).sum(0) + (bias if bias is not None else 0.0)
+            out[a0 + t] = acc * torch.sigmoid(acc)
+        conv_state[slot] = x[x.shape[0] - (taps - 1):]
+    return out
+
+
+def mamba2_prepare(proj, dt_off, dt_bias, a_log, x, heads, vdim):
+    T = proj.shape[0]
+    dt = torch.nn.functional.softplus(proj[:, dt_off:dt_off + heads].float() + (dt_bias if dt_bias is not None else 0.0),
+                                      threshold=30.0)
+    keep = torch.exp(-torch.exp(a_log) * dt)
+    return keep, (x[:, :heads * vdim].reshape(T, heads, vdim) * dt[:, :, None]).reshape(T, heads * vdim)
+
+
+def group_rms_norm(x, groups, n, group_stride, weight, eps, out_dtype, den_floor=None, skip=None, skip_w=None, skip_head=1,
+                   pre_gate=None, post_gate=None):
+    T, N = x.shape[0], groups * n
+    val = torch.stack([x[:, g * group_stride:g * group_stride + n] for g in range(groups)], 1)          # [T, groups, n]
+    if den_floor is not None:
+        den = torch.stack([x[:, g * group_stride + n] for g in range(groups)], 1)
+        val = val / (torch.maximum(den.abs(), den_floor) + 1e-6)[:, :, None]
+    val = val.reshape(T, N)
+    if skip is not None:
+        val = val + skip_w.repeat_interleave(skip_head)[:N] * skip[:, :N]
+    if pre_gate is not None:
+        g = pre_gate[:, :N].float()
+        val = val * g * torch.sigmoid(g)
+    y = _rms_unit(val.view(T, groups, n), eps).reshape(T, N)
+    if weight is not None:
+        y = y * weight
+    if post_gate is not None:
+        y = y * torch.sigmoid(post_gate[:, :N].float())
+    return y.to(out_dtype)
+
+
+def whole_norm_store(proj, q_off, k_off, v_off, q_w, k_w, eps, v_norm, slots, k_pages, v_pages, heads, kv_heads, dim, vdim, row,
+                     page_size):
+    T = proj.shape[0]
+    p = proj.float()
+    q, k = p[:, q_off:q_off + heads * dim], p[:, k_off:k_off + kv_heads * dim]
+    v = p[:, v_off:v_off + kv_heads * vdim].reshape(T, kv_heads, vdim)
+    if q_w is not None:
+        q = _rms_unit(q, eps) * q_w
+    if k_w is not None:
+        k = _rms_unit(k, eps) * k_w
+    if v_norm:
+        v = _rms_unit(v, eps)
+    pad = lambda t, d: torch.cat([t, torch.zeros(t.shape[0], t.shape[1], row - d)], 2)
+    q, k, v = pad(q.reshape(T, heads, dim), dim), pad(k.reshape(T, kv_heads, dim), dim), pad(v, vdim)
+    if slots is not None:
+        for t in range(T):
+            sl = int(slots[t])
+            if sl >= 0:
+                k_pages[sl // page_size, :, sl % page_size, :] = k[t].to(k_pages.dtype)
+                v_pages[sl // page_size, :, sl % page_size, :] = v[t].to(v_pages.dtype)
+    return q.reshape(T, heads * row).to(proj.dtype)
+
+
+NAMES = ["hyper_expand", "hyper_step", "scale_add_rows", "scaled_sum", "gated_linear_attention", "mlstm_prepare", "hgrn2_prepare",
+         "causal_conv_silu", "mamba2_prepare", "group_rms_norm", "whole_norm_store",
+         "activation", "qk_norm_rope_store", "sigmoid_gate", "decay_linear_attention", "gated_rms_norm", "post_add_norm", "scale_softcap", "latent_norm_store", "head_linear", "head_scale", "moe_route", "moe_experts",
          "embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
          "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "make_kv_tensor_map_2d", "tc_takes", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
          "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
