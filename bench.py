@@ -419,6 +419,10 @@ def random_model_on_device(raw, device="cuda:0", seed=0):
             t = torch.randn(p.shape, generator=g, device=device, dtype=torch.float32) * 0.02
             if p.init == "one_plus_normal":
                 t = t + 1.0
+            elif p.init == "identity":
+                t = t + torch.eye(p.shape[0], device=device)
+            elif p.init.startswith("const:"):
+                t = t + float(p.init[6:])
             b.part.assign(p.attr, t if p.kind == "vector" else t.to(torch.bfloat16))
     model.materialize(device, torch.bfloat16)
     return cfg, model
@@ -565,6 +569,30 @@ def zikupel_config(shape, layers):
     return dict(architecture="Zikupel", vocab=DESIGN_VOCAB, width=s["width"], norm=dict(eps=1e-5), layers=zl)
 
 
+def zazilix_config(shape, layers):
+    """The Zazilix design at the sizes of ``shape``, four residual streams: two layers of matrix memory (as many heads, keys
+    and values of the head size), one of chunked attention (chunks of 1,024 positions) beside forget-write linear attention
+    (half as many heads), one state-space layer (inner size twice the width in heads of 64, a state of 128); every layer
+    routes ``top`` of ``experts`` + 2 router outputs (the experts together as wide as the dense feed-forward of the shape)
+    beside a shared expert of one expert's size."""
+    s = DESIGN_SHAPES[shape]
+    H, d, W = s["heads"], s["head"], s["width"]
+    mem = dict(heads=H, dim=d, vdim=d, gate_cap=15.0)
+    par = dict(left=dict(heads=H, kv_heads=s["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, mask=dict(size=1024)),
+               right=dict(heads=H // 2, dim=d, vdim=d), left_scale=0.5, right_scale=0.5)
+    ssm = dict(heads=2 * W // 64, vdim=64, state=128, groups=2, conv=4, norm_groups=2)
+    moe = dict(kind="moe", expert=dict(ff=s["ff"] // s["top"]), router=dict(experts=s["experts"], top=s["top"], scale=1.0, identity=2),
+               shared=dict(ff=s["ff"] // s["top"]))
+    kinds = [("mlstm", mem), ("mlstm", mem), ("parallel", par), ("mamba2", ssm)]
+    zl = [dict(type=kinds[i % 4][0], mixer=dict(kinds[i % 4][1]), mlp=moe) for i in range(layers)]
+    return dict(architecture="Zazilix", vocab=DESIGN_VOCAB, width=W, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
+                max_positions=8192, streams=4, layers=zl)
+
+
+# the model a design is measured beside: the closest one the package had before it
+DESIGN_BESIDE = {"zapipel": "qwen2", "zikupel": "qwen2", "zazilix": "zikupel"}
+
+
 def design_configs(shape, layers):
     s = DESIGN_SHAPES[shape]
     mixer = dict(heads=s["heads"], dim=s["head"], vdim=s["head"], q_rank=s["q_rank"], kv_rank=s["kv_rank"],
@@ -582,7 +610,7 @@ def design_configs(shape, layers):
     qwen = dict(MODEL, vocab_size=DESIGN_VOCAB, hidden_size=s["width"], num_hidden_layers=layers,
                 num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["head"],
                 intermediate_size=s["ff"], tie_word_embeddings=False)
-    return {"zapipel": zap, "qwen2": qwen, "zikupel": zikupel_config(shape, layers)}
+    return {"zapipel": zap, "qwen2": qwen, "zikupel": zikupel_config(shape, layers), "zazilix": zazilix_config(shape, layers)}
 
 
 def run_design(args):
@@ -597,7 +625,7 @@ def run_design(args):
     context = args.context or 2048
     batches = [args.batch] if args.batch else [8, 64]
     shapes = sorted(DESIGN_SHAPES) if args.shape == "all" else [args.shape]
-    archs = [args.design, "qwen2"] if args.arch == "both" else [args.arch]
+    archs = [args.design, DESIGN_BESIDE[args.design]] if args.arch == "both" else [args.arch]
     out = {"design": args.design, "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
            "layers": layers, "vocab": DESIGN_VOCAB, "context": context, "peaks": pk["source"], "shapes": {}}
     sampler = ClockSampler()
@@ -737,11 +765,12 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase only and print a short line (for profiling; not a bench value)")
-    ap.add_argument("--design", choices=["zapipel", "zikupel"], default=None,
-                    help="the named design beside the Qwen2 decoder at equal sizes (prefill and decode); not the default run")
+    ap.add_argument("--design", choices=["zapipel", "zikupel", "zazilix"], default=None,
+                    help="the named design beside the closest earlier model at equal sizes (zapipel, zikupel: the Qwen2 decoder; "
+                         "zazilix: zikupel), prefill and decode; not the default run")
     ap.add_argument("--shape", choices=sorted(DESIGN_SHAPES) + ["all"], default="all", help="with --design: which sizes")
-    ap.add_argument("--arch", choices=["zapipel", "zikupel", "qwen2", "both"], default="both",
-                    help="with --design: which model (both: the design and the Qwen2 decoder)")
+    ap.add_argument("--arch", choices=["zapipel", "zikupel", "zazilix", "qwen2", "both"], default="both",
+                    help="with --design: which model (both: the design and the model it is measured beside)")
     ap.add_argument("--micro", action="store_true",
                     help="time single decode kernels replayed from a graph (skinny products, decode attention)")
     ap.add_argument("--profile-range", choices=["decode", "prefill"], default=None,

@@ -44,6 +44,8 @@ class Param:
     @property
     def shape(self) -> Tuple[int, ...]:
         first = self.pieces[0].shape
+        if not first:               # a single number
+            return ()
         return (sum(p.shape[0] for p in self.pieces),) + tuple(first[1:])
 
 

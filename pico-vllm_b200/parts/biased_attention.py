@@ -119,6 +119,13 @@ class ParallelMixers(Part):
         side, _, inner = attr.partition("__")
         getattr(self, side).assign(inner, tensor)
 
+    def __getattr__(self, attr: str):
+        """A parameter of one side under the name ``params`` gives it (``left__proj_weight``)."""
+        side, sep, inner = attr.partition("__")
+        if sep and side in ("left", "right") and inner:
+            return getattr(self.__dict__[side], inner)
+        raise AttributeError(attr)
+
     def cache_spec(self):
         return _as_tuple(self.left.cache_spec()) + _as_tuple(self.right.cache_spec())
 
