@@ -119,13 +119,17 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD_MAX / 8][4], const float (
 // ------------------------------------------------------------------------------------------ prefill
 // grid: (tiles of tokens, kv heads, listed segments).  A block takes `tpt` = 64 / g tokens of one
 // segment and the g query heads of one kv head: 64 rows, 16 per warp.
-template <int HD_MAX>
+// EXTRA: a distance bias slope_h * (query position - key position) taken off head h's scores, only
+// the keys of the query's own chunk of `chunk` positions (counted from the request's start; 0: all), and a sink, one more
+// term exp(sinks[h]) in the softmax's denominator that has no value (nullptr: none)
+template <int HD_MAX, bool EXTRA>
 __global__ void __launch_bounds__(MMA_THREADS)
 paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pages,
                          const bf16* __restrict__ v_pages, bf16* __restrict__ out, const int* __restrict__ seg_list,
                          const int* __restrict__ cu_q, const int* __restrict__ positions,
                          const int* __restrict__ block_table, int table_stride, int nh, int nkv, int hd,
-                         int page_size, int window, float scale_log2, float cap_log2, float cap_2x) {
+                         int page_size, int window, float scale_log2, float cap_log2, float cap_2x,
+                         const float* __restrict__ slopes, int chunk, const float* __restrict__ sinks) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -139,7 +143,8 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
     const int kh = blockIdx.y;
     const int pos0 = positions[q0] + tok0;          // position of the tile's first token
     const int hi = pos0 + ntok;                     // one past the last visible key of the tile
-    const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    if (EXTRA && chunk > 0) lo = max(lo, pos0 / chunk * chunk);     // the tile's first token has the lowest chunk start
     const int ld = hd + 8;
     const TileMap tm = make_tile_map(hd, page_size);
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);              // [64][ld]
@@ -168,12 +173,15 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     // positions of the two rows this thread holds
     int row_pos[2], row_lo[2];
+    float row_slope[2] = {0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = warp * 16 + (lane >> 2) + r * 8;
         const int tok = row / g;
         row_pos[r] = tok < ntok ? pos0 + tok : -1;             // -1: a padding row sees nothing
         row_lo[r] = (window > 0 && row_pos[r] + 1 > window) ? row_pos[r] + 1 - window : 0;
+        if (EXTRA && chunk > 0 && row_pos[r] >= 0) row_lo[r] = max(row_lo[r], row_pos[r] / chunk * chunk);
+        if (EXTRA && slopes) row_slope[r] = slopes[kh * g + row - tok * g] * 1.4426950408889634f;
     }
     // the last key any row of this warp sees: later tiles are skipped by this warp
     const int warp_last_tok = min(ntok - 1, (warp * 16 + 15) / g);
@@ -204,6 +212,7 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
                     const int r = e >> 1;
                     const bool vis = n <= row_pos[r] && n >= row_lo[r];
                     s[j][e] = vis ? pico_score_log2(s[j][e], scale_log2, cap_log2, cap_2x) : -INFINITY;
+                    if (EXTRA && vis) s[j][e] = fmaf(row_slope[r], (float)(n - row_pos[r]), s[j][e]);
                 }
             }
             online_softmax<HD_MAX, MMA_BN / 8>(s, m, l, o);
@@ -216,7 +225,9 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
         const int row = warp * 16 + (lane >> 2) + r * 8;
         const int tok = row / g, head = row - tok * g;
         if (tok >= ntok) continue;
-        const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+        float den = l[r];
+        if (EXTRA && sinks) den += fast_exp2(sinks[kh * g + head] * 1.4426950408889634f - m[r]);      // the sink in the frame of this row's maximum
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
         bf16* dst = out + ((size_t)(q0 + tok0 + tok) * nh + kh * g + head) * hd + (lane & 3) * 2;
 #pragma unroll
         for (int i = 0; i < HD_MAX / 8; ++i)
@@ -228,14 +239,15 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
 // ------------------------------------------------------------------------------------------ decode
 // grid: (splits, kv heads, listed tokens).  One token, the g (<= 16) query heads of one kv head:
 // a single 16-row tile.  Warp w takes cache positions 16w .. 16w+15 of every 64-position tile.
-template <int HD_MAX>
+template <int HD_MAX, bool EXTRA>
 __global__ void __launch_bounds__(MMA_THREADS)
 paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pages,
                         const bf16* __restrict__ v_pages, bf16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, const int* __restrict__ tok_list,
                         const int* __restrict__ tok_seg, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_stride, int nh, int nkv, int hd,
-                        int page_size, int window, float scale_log2, int n_splits, float cap_log2, float cap_2x) {
+                        int page_size, int window, float scale_log2, int n_splits, float cap_log2, float cap_2x,
+                        const float* __restrict__ slopes, int chunk, const float* __restrict__ sinks) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -245,7 +257,8 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos = positions[t];
     const int hi = pos + 1;                         // pos = -1 (padding): no keys at all
-    const int lo = (window > 0 && hi > window) ? hi - window : 0;
+    int lo = (window > 0 && hi > window) ? hi - window : 0;
+    if (EXTRA && chunk > 0 && pos >= 0) lo = max(lo, pos / chunk * chunk);
     const int ntiles_all = (hi - lo + MMA_BN - 1) / MMA_BN;
     const int per = (ntiles_all + n_splits - 1) / n_splits;
     const int begin = lo + sp * per * MMA_BN;
@@ -279,6 +292,14 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
 #pragma unroll
     for (int i = 0; i < HD_MAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float row_slope[2] = {0.f, 0.f};
+    if (EXTRA && slopes) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = (lane >> 2) + r * 8;
+            if (row < g) row_slope[r] = slopes[kh * g + row] * 1.4426950408889634f;
+        }
+    }
 
     for (int it = 0; it < ntiles; ++it) {
         const int n0 = begin + it * MMA_BN;
@@ -306,6 +327,7 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                 for (int e = 0; e < 4; ++e) {
                     const int n = w0 + j * 8 + (lane & 3) * 2 + (e & 1);
                     s[j][e] = n < end ? pico_score_log2(s[j][e], scale_log2, cap_log2, cap_2x) : -INFINITY;
+                    if (EXTRA && n < end) s[j][e] = fmaf(row_slope[e >> 1], (float)(n - pos), s[j][e]);
                 }
             online_softmax<HD_MAX, 2>(s, m, l, o);
             pv_tile<HD_MAX, 2>(o, s, v_s + (buf * MMA_BN + warp * 16) * ld, hd, ld, lane);
@@ -349,6 +371,13 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
             }
         }
         const int h = kh * g + row;
+        if (EXTRA && sinks && sp == 0 && pos >= 0) {      // the sink joins the first part: one more term of its denominator
+            const float sk = sinks[h] * 1.4426950408889634f, mm = fmaxf(M, sk);
+            const float f = M == -INFINITY ? 0.f : exp2f(M - mm);
+            L = L * f + exp2f(sk - mm);
+            acc *= f;
+            M = mm;
+        }
         if (n_splits == 1) {
             out[((size_t)t * nh + h) * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         } else {
@@ -418,8 +447,11 @@ static size_t decode_smem(int hd) {
 PICO_API int pico_paged_prefill_mma(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                     void* out, const int* seg_list, int n_segs, const int* cu_q, int max_q_len,
                                     const int* positions, const int* block_table, int table_stride, int nh,
-                                    int nkv, int hd, int page_size, int window, float scale, float softcap, cudaStream_t stream) {
+                                    int nkv, int hd, int page_size, int window, float scale, float softcap,
+                                    const float* slopes, int chunk, const float* sinks, cudaStream_t stream) {
     if (n_segs <= 0 || max_q_len <= 0) return 0;
+    if (chunk < 0) return PICO_ERR_SIZE;
+    const bool extra = slopes || chunk > 0 || sinks;
     if (hd % 16 != 0 || hd < 16 || hd > 256 || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
     if (g > 64 || nkv > 65535 || n_segs > 65535) return PICO_ERR_SIZE;
@@ -429,16 +461,19 @@ PICO_API int pico_paged_prefill_mma(const void* q, int q_row_stride, const void*
     const size_t smem = prefill_smem(hd);
     const float scale_log2 = scale * 1.4426950408889634f;
     const float cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, cap_2x = softcap > 0.f ? 2.0f * scale / softcap : 0.f;
-#define LAUNCH_PREFILL(HD)                                                                                          \
+#define LAUNCH_PREFILL_X(HD, X)                                                                                     \
     do {                                                                                                            \
-        cudaFuncSetAttribute(paged_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        pico_launch((paged_prefill_mma_kernel<HD>), dim3(grid), dim3(MMA_THREADS), smem, stream,                                           \
+        cudaFuncSetAttribute(paged_prefill_mma_kernel<HD, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        pico_launch((paged_prefill_mma_kernel<HD, X>), dim3(grid), dim3(MMA_THREADS), smem, stream,                 \
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, seg_list, cu_q,   \
-            positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale_log2, cap_log2, cap_2x);    \
+            positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale_log2, cap_log2, cap_2x,     \
+            slopes, chunk, sinks);                                                                        \
     } while (0)
+#define LAUNCH_PREFILL(HD) do { if (extra) LAUNCH_PREFILL_X(HD, true); else LAUNCH_PREFILL_X(HD, false); } while (0)
     if (hd <= 64) LAUNCH_PREFILL(64);
     else if (hd <= 128) LAUNCH_PREFILL(128);
     else LAUNCH_PREFILL(256);
+#undef LAUNCH_PREFILL_X
 #undef LAUNCH_PREFILL
     return pico_launch_status();
 }
@@ -450,8 +485,11 @@ PICO_API int pico_paged_decode_mma(const void* q, int q_row_stride, const void* 
                                    void* out, float* part_o, float* part_ml, const int* tok_list, int n_tok,
                                    const int* tok_seg, const int* positions, const int* block_table,
                                    int table_stride, int nh, int nkv, int hd, int page_size, int window,
-                                   float scale, int n_splits, float softcap, cudaStream_t stream) {
+                                   float scale, int n_splits, float softcap, const float* slopes, int chunk,
+                                   const float* sinks, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
+    if (chunk < 0) return PICO_ERR_SIZE;
+    const bool extra = slopes || chunk > 0 || sinks;
     if (hd % 16 != 0 || hd < 16 || hd > 256 || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
     if (g > 16 || nkv > 65535 || n_tok > 65535 || n_splits < 1 || n_splits > COMBINE_MAX_SPLITS) return PICO_ERR_SIZE;
@@ -461,17 +499,19 @@ PICO_API int pico_paged_decode_mma(const void* q, int q_row_stride, const void* 
     const size_t smem = decode_smem(hd);
     const float scale_log2 = scale * 1.4426950408889634f;
     const float cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, cap_2x = softcap > 0.f ? 2.0f * scale / softcap : 0.f;
-#define LAUNCH_DECODE(HD)                                                                                          \
+#define LAUNCH_DECODE_X(HD, X)                                                                                     \
     do {                                                                                                           \
-        cudaFuncSetAttribute(paged_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        pico_launch((paged_decode_mma_kernel<HD>), dim3(grid), dim3(MMA_THREADS), smem, stream,                                           \
+        cudaFuncSetAttribute(paged_decode_mma_kernel<HD, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        pico_launch((paged_decode_mma_kernel<HD, X>), dim3(grid), dim3(MMA_THREADS), smem, stream,                 \
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, part_o, part_ml, \
             tok_list, tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale_log2,   \
-            n_splits, cap_log2, cap_2x);                                                                           \
+            n_splits, cap_log2, cap_2x, slopes, chunk, sinks);                                           \
     } while (0)
+#define LAUNCH_DECODE(HD) do { if (extra) LAUNCH_DECODE_X(HD, true); else LAUNCH_DECODE_X(HD, false); } while (0)
     if (hd <= 64) LAUNCH_DECODE(64);
     else if (hd <= 128) LAUNCH_DECODE(128);
     else LAUNCH_DECODE(256);
+#undef LAUNCH_DECODE_X
 #undef LAUNCH_DECODE
     if (n_splits > 1) return pico_launch_decode_combine(part_o, part_ml, out, tok_list, n_tok, nh, hd, n_splits, stream);
     return pico_launch_status();

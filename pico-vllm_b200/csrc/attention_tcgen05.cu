@@ -179,7 +179,9 @@ __device__ __forceinline__ void tca_softmax_sync() { asm volatile("bar.sync 2, 2
 #define TCA_COL_Q 448          // the queries as a tensor-memory operand: 64 columns of bfloat16 pairs at head size 128
 
 // CAP: the scaled scores pass through a soft cap c * tanh(s / c) before the softmax (cap_log2 = c log2 e, cap_2x = 2 scale / c)
-template <int HD, bool CAP>      // head size, a multiple of 64 up to 128
+// EXTRA (without CAP): a distance bias slope_h * (query position - key position) taken off head h's scores, only the keys of the query's own chunk of `chunk` positions (counted from the request's start; 0: all), and a sink,
+// one more term exp(sinks[h]) in the softmax's denominator that has no value (nullptr: none)
+template <int HD, bool CAP, bool EXTRA>      // head size, a multiple of 64 up to 128
 __global__ void __launch_bounds__(TCA_THREADS)
 paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out,
@@ -187,7 +189,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              const int* __restrict__ positions, const int* __restrict__ block_table, int table_stride,
                              int nh, int nkv, int page_size, int window, float scale_log2, float cap_log2, float cap_2x,
                              float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
-                             size_t n_rows, int n_parts, int split_min) {
+                             size_t n_rows, int n_parts, int split_min, const float* __restrict__ slopes, int chunk,
+                             const float* __restrict__ sinks) {
     pdl_launch_dependents();
     extern __shared__ unsigned char tca_dyn[];
     constexpr int NH = HD / 64;                              // 64-dim blocks of a head
@@ -250,7 +253,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     const int ntok = tile_ok ? min(tpt, qlen - tok0) : 0;
     const int pos0 = tile_ok ? positions[q0] + tok0 : 0;     // position of the tile's first token
     const int hi = pos0 + ntok;                              // one past the last visible key of the tile
-    const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    if (EXTRA && chunk > 0) lo = max(lo, pos0 / chunk * chunk);      // the tile's first token has the lowest chunk start
     int t_begin = lo / TCA_BN, t_end = tile_ok ? (hi + TCA_BN - 1) / TCA_BN : 0;
     const bool split = n_parts == 2 && tile_ok && t_end - t_begin >= split_min;
     if (split) {
@@ -380,7 +384,9 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const int tok = r / g, head = r - tok * g;
         const bool row_ok = tok < ntok;
         const int row_pos = row_ok ? pos0 + tok : -1;
-        const int row_lo = (window > 0 && row_pos + 1 > window) ? row_pos + 1 - window : 0;
+        int row_lo = (window > 0 && row_pos + 1 > window) ? row_pos + 1 - window : 0;
+        if (EXTRA && chunk > 0 && row_ok) row_lo = max(row_lo, row_pos / chunk * chunk);
+        const float slope2 = (EXTRA && slopes) ? slopes[kh * g + head] * 1.4426950408889634f : 0.f;     // log2 units
         const uint32_t lane_off = (uint32_t)(qtr * 32) << 16;
         const uint32_t tmem_s = tmem_base + TCA_COL_S + pipe * TCA_BN + lane_off;
         const uint32_t tmem_p = tmem_base + TCA_COL_P + pipe * (TCA_BN / 2) + lane_off;
@@ -436,6 +442,12 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
                     if (!(n <= row_pos && n >= row_lo)) sv[c] = 0xff800000u;     // -inf
                 }
             }
+            if (EXTRA) {     // scores in log2 units with the distance bias taken off; a hidden key stays at -inf
+                const float base = fmaf(slope2, (float)(n0 - row_pos), 0.f);
+#pragma unroll
+                for (int c = 0; c < 64; ++c)
+                    sv[c] = __float_as_uint(fmaf(__uint_as_float(sv[c]), scale_log2, fmaf(slope2, (float)c, base)));
+            }
             // the maximum of the raw scores (the scale is positive), four chains of three-input maxima
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -447,7 +459,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
             const float mx_raw = fmaxf(tca_max3(mx4[0], mx4[1], mx4[2]), mx4[3]);
             // the cap is monotonic, so the capped maximum is the cap of the maximum; a row with no visible key stays at -inf
             const float mx = CAP ? (mx_raw == -INFINITY ? -INFINITY : pico_score_log2(mx_raw, scale_log2, cap_log2, cap_2x))
-                                 : mx_raw * scale_log2;
+                                 : EXTRA ? mx_raw : mx_raw * scale_log2;
             // the maximum in use moves only when the true one has grown by more than 2^8: the same
             // value is used for the probabilities and for the sum, so the result is exact
             const bool grow = mx > m_use + TCA_RESCALE_AT;
@@ -473,7 +485,9 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
                         if (sv[c] == 0xff800000u) x0 = -INFINITY;
                         if (sv[c + 1] == 0xff800000u) x1 = -INFINITY;
                     }
-                } else
+                } else if (EXTRA)
+                    tca_unpack(tca_add2(tca_pack(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), neg_m2), x0, x1);
+                else
                     tca_unpack(tca_fma2(tca_pack(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
                 const float p0 = tca_exp2(x0), p1 = tca_exp2(x1);
                 sum2[(c >> 1) & 1] = tca_add2(sum2[(c >> 1) & 1], tca_pack(p0, p1));
@@ -609,9 +623,19 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
                     w_other = f2 * inv2;
                 }
             } else {
-                const float inv = den > 0.f ? 1.0f / den : 0.f;
+                float all = den;
+                if (EXTRA && sinks && m != -INFINITY) {      // the sink: a term of the denominator only (m may lie far below it)
+                    const float sk = sinks[kh * g + head] * 1.4426950408889634f;
+                    const float mm = fmaxf(m, sk), f1 = tca_exp2(m - mm);
+                    all = den * f1 + tca_exp2(sk - mm);
+                    wa = fa * f1;
+                    wb = fb * f1;
+                }
+                const float inv = all > 0.f ? 1.0f / all : 0.f;
+                if (EXTRA && sinks && m != -INFINITY) { wa *= inv; wb *= inv; } else {
                 wa = fa * inv;
                 wb = fb * inv;
+                }
             }
             if (write_out) {
 #pragma unroll 1
@@ -711,13 +735,17 @@ PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, co
                                         const int* seg_list, int n_segs, const int* cu_q, int max_q_len,
                                         const int* positions, const int* block_table, int table_stride, int nh, int nkv,
                                         int hd, int page_size, int window, float scale, int pair_min_keys, float* scratch,
-                                        int n_tokens, int* counters, int n_counters, float softcap, cudaStream_t stream) {
+                                        int n_tokens, int* counters, int n_counters, float softcap, const float* slopes,
+                                        int chunk, const float* sinks, cudaStream_t stream) {
     if (n_segs <= 0 || max_q_len <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
     if (g > TCA_BM || nkv > 65535 || n_segs > 65535) return PICO_ERR_SIZE;
     if (page_size < 8 || TCA_BN % page_size != 0) return PICO_ERR_SIZE;
     if (q_row_stride % 8 != 0) return PICO_ERR_ALIGN;
+    const bool extra = slopes || chunk > 0 || sinks;
+    if (chunk < 0 || (extra && softcap > 0.f)) return PICO_ERR_SIZE;       // the bias is not built together with the cap
+    if (extra) pair_min_keys = 0;                                          // nor with tiles shared by two blocks
     const int tpt = TCA_BM / g;
     const int n_qt = (max_q_len + tpt - 1) / tpt;
     const int n_parts = (pair_min_keys > 0 && scratch && counters && (long long)n_qt * nkv * n_segs <= n_counters && n_tokens > 0) ? 2 : 1;
@@ -732,15 +760,15 @@ PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, co
     CUtensorMap km, vm;
     memcpy(&km, k_map, sizeof(CUtensorMap));
     memcpy(&vm, v_map, sizeof(CUtensorMap));
-#define LAUNCH_TCA(HD, CAP)                                                                                              \
+#define LAUNCH_TCA(HD, CAP, EXTRA)                                                                                              \
     do {                                                                                                                 \
-        cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<HD, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        pico_launch((paged_prefill_tcgen05_kernel<HD, CAP>), grid, dim3(TCA_THREADS), smem, stream, km, vm, (const bf16*)q, \
+        cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<HD, CAP, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        pico_launch((paged_prefill_tcgen05_kernel<HD, CAP, EXTRA>), grid, dim3(TCA_THREADS), smem, stream, km, vm, (const bf16*)q, \
                     q_row_stride, (bf16*)out, seg_list, cu_q, positions, block_table, table_stride, nh, nkv, page_size,  \
-                    window, scale_log2, cap_log2, cap_2x, part_o, part_ml, counters, n_rows, n_parts, split_min);        \
+                    window, scale_log2, cap_log2, cap_2x, part_o, part_ml, counters, n_rows, n_parts, split_min, slopes, chunk, sinks); \
     } while (0)
-    if (hd == 64) { if (cap_log2 > 0.f) LAUNCH_TCA(64, true); else LAUNCH_TCA(64, false); }
-    else { if (cap_log2 > 0.f) LAUNCH_TCA(128, true); else LAUNCH_TCA(128, false); }
+    if (hd == 64) { if (extra) LAUNCH_TCA(64, false, true); else if (cap_log2 > 0.f) LAUNCH_TCA(64, true, false); else LAUNCH_TCA(64, false, false); }
+    else { if (extra) LAUNCH_TCA(128, false, true); else if (cap_log2 > 0.f) LAUNCH_TCA(128, true, false); else LAUNCH_TCA(128, false, false); }
 #undef LAUNCH_TCA
     return pico_launch_status();
 }

@@ -84,6 +84,7 @@ gated_linear_attention_kernel(const float* __restrict__ q, int q_stride, const f
         }
     }
     float* mypart = part + (size_t)warp * GL_TOK * 32 * GL_COLS;
+    const bool live = col0 < dv;                       // uniform for the warp
     for (int t0 = t_begin; t0 < t_end; t0 += GL_TOK) {
         const int nt = min(GL_TOK, t_end - t0);
         __syncthreads();                               // everyone is done with the tokens before
@@ -100,6 +101,7 @@ gated_linear_attention_kernel(const float* __restrict__ q, int q_stride, const f
             vs[idx] = j < dv ? v[(size_t)(t0 + tt) * v_stride + (size_t)h * dv + j] : 0.f;
         }
         __syncthreads();
+        if (!live) continue;                           // a warp past the last column only helps to load
         for (int tt = 0; tt < nt; ++tt) {
             const float4 va = *reinterpret_cast<const float4*>(vs + tt * GL_WARPS * GL_COLS + warp * GL_COLS);
             const float4 vb = *reinterpret_cast<const float4*>(vs + tt * GL_WARPS * GL_COLS + warp * GL_COLS + 4);

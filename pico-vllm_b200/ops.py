@@ -54,9 +54,10 @@ def library():
         "pico_rope_store": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
         "pico_paged_attention_generic": [vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                                          i32, i32, f32, i32, f32, i32, vp, i32, vp, vp],
-        "pico_paged_prefill_mma": [vp, i32, vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp],
+        "pico_paged_prefill_mma": [vp, i32, vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp, i32,
+                                   vp, vp],
         "pico_paged_decode_mma": [vp, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
-                                  f32, i32, f32, vp],
+                                  f32, i32, f32, vp, i32, vp, vp],
         "pico_skinny_linear": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp, vp],
         "pico_skinny_argmax": [vp, i32, vp, vp, i32, i32, i32, vp, f32, vp, vp],
         "pico_skinny_norm_fits": [i32, i32],
@@ -70,7 +71,7 @@ def library():
         "pico_tma_status": [vp],
         "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32, i32],
         "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32,
-                                       vp, i32, vp, i32, f32, vp],
+                                       vp, i32, vp, i32, f32, vp, i32, vp, vp],
         "pico_tca_status": [vp],
         "pico_gemm_tcgen05_pair": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],
         "pico_tp_status": [vp],
@@ -395,7 +396,8 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                         n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
                         scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
                         k_map=None, v_map=None, k_map2d=None, v_map2d=None, pair_min_keys: int = 0,
-                        softcap: Optional[float] = None) -> torch.Tensor:
+                        softcap: Optional[float] = None, slopes: Optional[torch.Tensor] = None,
+                        chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same attention as :func:`paged_attention` for bfloat16 on tensor cores, in two launches:
     segments that bring two or more tokens (``prefill_segs`` int32 [n_prefill_segs], None = all
     segments; ``cu_q`` int32 [segments + 1]; ``max_prefill_q`` their longest) and single tokens
@@ -403,7 +405,9 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     cut into ``n_splits`` parts.  Every token of the batch must be in exactly one of the two.
     With ``k_map`` / ``v_map`` (from :func:`make_kv_tensor_map` over these same pages) the single
     tokens run in the kernel that brings pages in by TMA; with ``k_map2d`` / ``v_map2d`` (from
-    :func:`make_kv_tensor_map_2d`) the portions run on the tcgen05 tensor cores."""
+    :func:`make_kv_tensor_map_2d`) the portions run on the tcgen05 tensor cores.
+    ``slopes``, ``chunk`` and ``sinks`` as in :func:`paged_attention` (not together with ``softcap``); with them the
+    single tokens run in the kernel that reads pages through the block table."""
     _cuda(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs, decode_tokens, scratch)
     T = q.shape[0]
     if not mma_attention_takes(q.dtype, n_heads, n_kv_heads, head_dim):
@@ -420,9 +424,19 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     for t in (tok_seg, positions, block_table, cu_q, prefill_segs, decode_tokens):
         if t is not None and t.dtype != torch.int32:
             raise KernelError("paged_attention_mma: index tensors must be int32")
+    _cuda(slopes, sinks)
+    for t in (slopes, sinks):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (n_heads,)):
+            raise KernelError("paged_attention_mma: slopes and sinks must be float32 [n_heads]")
     lib = library()
     win = int(window) if window else 0
     cap = float(softcap) if softcap else 0.0
+    chunk = int(chunk) if chunk else 0
+    extra = slopes is not None or sinks is not None or chunk > 0
+    if extra and cap > 0.0:
+        raise KernelError("paged_attention_mma: a distance bias, chunks or a sink are not built together with a soft cap")
+    if extra:
+        k_map = v_map = None
     if n_prefill_segs > 0 and k_map2d is not None and v_map2d is not None:
         # pair_min_keys > 0 (and scratch for two partial results per (token, head)): every query tile gets two
         # blocks, which share it when it sees at least that many keys; the pairs' counters are zero between launches
@@ -436,14 +450,15 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                                               n_kv_heads, head_dim, page_size, win, float(scale),
                                               int(pair_min_keys) if split else 0, _ptr(scratch) if split else None, T,
                                               _ptr(counters) if split else None, counters.numel() if split else 0,
-                                              cap, _stream()),
+                                              cap, _ptr(slopes), chunk, _ptr(sinks), _stream()),
                f"paged_prefill_tcgen05 (head_dim {head_dim})")
         _count()
     elif n_prefill_segs > 0:
         _check(lib.pico_paged_prefill_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out),
                                           _ptr(prefill_segs), n_prefill_segs, _ptr(cu_q), max_prefill_q,
                                           _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
-                                          n_kv_heads, head_dim, page_size, win, float(scale), cap, _stream()),
+                                          n_kv_heads, head_dim, page_size, win, float(scale), cap, _ptr(slopes), chunk,
+                                          _ptr(sinks), _stream()),
                f"paged_prefill_mma (head_dim {head_dim})")
         _count()
     if n_decode_tokens > 0:
@@ -466,7 +481,7 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                                              part_ml, _ptr(decode_tokens), n_decode_tokens, _ptr(tok_seg),
                                              _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
                                              n_kv_heads, head_dim, page_size, win, float(scale), n_splits, cap,
-                                             _stream()),
+                                             _ptr(slopes), chunk, _ptr(sinks), _stream()),
                    f"paged_decode_mma (head_dim {head_dim})")
         clustered = k_map is not None and v_map is not None and n_splits in (2, 4, 8, 16)
         _count(2 if n_splits > 1 and not clustered else 1)

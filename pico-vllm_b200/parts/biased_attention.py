@@ -89,9 +89,16 @@ class DistanceBiasAttention(Part):
         out = torch.empty((h.shape[0], H * row), dtype=h.dtype, device=h.device)
         plan = batch.plan(self)
         splits = plan.splits if plan is not None else 1
-        ops.paged_attention(q, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table, H, G, row,
-                            cache.page_size, self.window, self.scale, splits, batch.scratch, slopes=self.slopes,
-                            chunk=self.chunk, sinks=self.sinks)
+        if ops.mma_attention_takes(h.dtype, H, G, row):
+            ops.paged_attention_mma(q, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table, batch.cu_q,
+                                    batch.prefill_segs, batch.num_prefill_segs, batch.max_prefill_q, batch.decode_tokens,
+                                    batch.num_decode_tokens, H, G, row, cache.page_size, self.window, self.scale, splits,
+                                    batch.scratch, None, None, cache.k_map2d, cache.v_map2d, 0, slopes=self.slopes,
+                                    chunk=self.chunk, sinks=self.sinks)
+        else:       # float32, or sizes the tensor-core kernels do not take
+            ops.paged_attention(q, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table, H, G, row,
+                                cache.page_size, self.window, self.scale, splits, batch.scratch, slopes=self.slopes,
+                                chunk=self.chunk, sinks=self.sinks)
         return _linear(out, self.o_weight)
 
 

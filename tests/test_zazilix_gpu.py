@@ -11,6 +11,7 @@ routing in bfloat16 is covered by the router kernel's own test.
 """
 import copy
 import json
+import math
 import os
 import subprocess
 import sys
@@ -532,6 +533,72 @@ def test_norm_store_and_biased_attention_kernels(dtype, H, G, d, dv, ps, chunk):
         ops.paged_attention(qd, kp, vp, out, dev(seg), dev(pos), dev(table), H, G, row, ps, None, 0.3, splits, scratch,
                             slopes=dev(slopes.float()), chunk=chunk or None, sinks=torch.zeros(H, device=DEV))
         _close(out.view(T, H, row), want, dtype, f"attention in {splits} parts")
+    _status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,G,d,ps,chunk,window", [(4, 2, 64, 16, 100, None), (8, 2, 128, 16, 192, None), (2, 1, 128, 64, 0, None),
+                                                   (6, 2, 48, 8, 70, None), (16, 1, 32, 4, 33, 50), (4, 4, 80, 16, 128, None),
+                                                   (2, 2, 64, 32, 64, 40)])
+def test_biased_attention_on_tensor_cores(H, G, d, ps, chunk, window):
+    """The bfloat16 kernels: portions of prompts (with tensor maps over the pages where the head size has them) beside
+    single tokens in one and in four parts, over pages in any order that hold NaN wherever nothing was stored.  Sinks
+    differ by head; requests start in the middle of a chunk, cross chunk borders and are longer than one tile of keys."""
+    from pico_vllm_b200 import ops
+    g = torch.Generator().manual_seed(H * 131 + d + chunk)
+    # (keys already cached, tokens the step brings)
+    reqs = [(0, 150), (97, 1), (60, 141), (299, 1), (chunk or 77, 2), (max(chunk - 1, 0), 1), (0, 1), (130, 70)]
+    total = [a + b for a, b in reqs]
+    n_pages = sum(-(-n // ps) for n in total) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.zeros(len(reqs), max(-(-n // ps) for n in total) + 1, dtype=torch.int32)
+    kp = torch.full((n_pages, G, ps, d), float("nan"), dtype=torch.bfloat16)
+    vp = torch.full_like(kp, float("nan"))
+    K = [torch.randn(n, G, d, generator=g).to(torch.bfloat16) for n in total]
+    V = [torch.randn(n, G, d, generator=g).to(torch.bfloat16) for n in total]
+    for s, n in enumerate(total):
+        for b in range(-(-n // ps)):
+            table[s, b] = order.pop()
+            m = min(ps, n - b * ps)
+            kp[table[s, b], :, :m] = K[s][b * ps:b * ps + m].transpose(0, 1)
+            vp[table[s, b], :, :m] = V[s][b * ps:b * ps + m].transpose(0, 1)
+    seg, pos, cu = [], [], [0]
+    for s, (a, b) in enumerate(reqs):
+        seg += [s] * b
+        pos += list(range(a, a + b))
+        cu.append(cu[-1] + b)
+    T = len(seg)
+    q = (torch.randn(T, H * d + 16, generator=g) * 1.5).to(torch.bfloat16)
+    slopes = torch.tensor([2.0 ** (-8.0 * (a + 1) / H) for a in range(H)])
+    sinks = torch.linspace(-1.0, 2.0, H)
+    want = torch.zeros(T, H, d, dtype=torch.float64)
+    for t in range(T):
+        s, i = seg[t], pos[t]
+        lo = (i // chunk) * chunk if chunk else 0
+        if window:
+            lo = max(lo, i + 1 - window)
+        for a in range(H):
+            kk, vv = K[s][lo:i + 1, a // (H // G)].double(), V[s][lo:i + 1, a // (H // G)].double()
+            sc = (kk @ q[t, a * d:(a + 1) * d].double()) * 0.11 - float(slopes[a]) * (i - torch.arange(lo, i + 1)).double()
+            e = torch.exp(sc)
+            want[t, a] = (e / (math.exp(float(sinks[a])) + e.sum())) @ vv
+    dev = lambda x: x.to(DEV)
+    kd, vd = dev(kp), dev(vp)
+    pre = [s for s, (a, b) in enumerate(reqs) if b > 1]
+    dec = [cu[s] for s, (a, b) in enumerate(reqs) if b == 1]
+    for maps in (False, True):
+        k2, v2 = (ops.make_kv_tensor_map_2d(kd), ops.make_kv_tensor_map_2d(vd, values=True)) if maps else (None, None)
+        if maps and (k2 is None or v2 is None):
+            continue
+        for splits in (1, 4):
+            out = torch.full((T, H * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+            scratch = torch.empty(ops.attention_scratch_floats(T, H, d, splits), dtype=torch.float32, device=DEV)
+            ops.paged_attention_mma(dev(q), kd, vd, out, dev(torch.tensor(seg, dtype=torch.int32)),
+                                    dev(torch.tensor(pos, dtype=torch.int32)), dev(table), dev(torch.tensor(cu, dtype=torch.int32)),
+                                    dev(torch.tensor(pre, dtype=torch.int32)), len(pre), max(b for a, b in reqs),
+                                    dev(torch.tensor(dec, dtype=torch.int32)), len(dec), H, G, d, ps, window, 0.11, splits, scratch,
+                                    None, None, k2, v2, 0, slopes=dev(slopes.float()), chunk=chunk or None, sinks=dev(sinks.float()))
+            _close(out.view(T, H, d), want, torch.bfloat16, f"tensor maps {maps}, {splits} parts")
     _status()
 
 
