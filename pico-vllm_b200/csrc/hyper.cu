@@ -14,14 +14,49 @@
 
 #define HC_MAX_STREAMS 8
 
-template <typename TA>
+// V consecutive coordinates a thread (4: 16-byte accesses, when the width is a multiple of four)
+template <int V>
+__device__ __forceinline__ void hc_load(const float* p, float (&o)[V]) {
+    if constexpr (V == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    } else
+        o[0] = *p;
+}
+template <int V>
+__device__ __forceinline__ void hc_load(const bf16* p, float (&o)[V]) {
+    if constexpr (V == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+        o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+    } else
+        o[0] = __bfloat162float(*p);
+}
+template <int V>
+__device__ __forceinline__ void hc_store(float* p, const float (&o)[V]) {
+    if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+    else *p = o[0];
+}
+template <int V>
+__device__ __forceinline__ void hc_store(bf16* p, const float (&o)[V]) {
+    if constexpr (V == 4) {
+        uint2 v;
+        *reinterpret_cast<__nv_bfloat162*>(&v.x) = __floats2bfloat162_rn(o[0], o[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&v.y) = __floats2bfloat162_rn(o[2], o[3]);
+        *reinterpret_cast<uint2*>(p) = v;
+    } else
+        *p = __float2bfloat16_rn(o[0]);
+}
+
+template <typename TA, int V>
 __global__ void __launch_bounds__(256)
 hyper_step_kernel(float* __restrict__ x, const TA* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ outw,
                   const float* __restrict__ inw, const float* __restrict__ norm_w, float eps, TA* __restrict__ h,
                   const int* __restrict__ rows, float* __restrict__ sum_out, int S, int D) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float hu[];                 // u [D]
+    extern __shared__ __align__(16) float hu[];   // u [D]
     __shared__ float scratch[33];
     __shared__ float s_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], s_out[HC_MAX_STREAMS], s_in[HC_MAX_STREAMS];
     const int r = blockIdx.x;
@@ -34,41 +69,74 @@ hyper_step_kernel(float* __restrict__ x, const TA* __restrict__ y, const float* 
     __syncthreads();
     float* xt = x + t * (size_t)S * D;
     float ss = 0.f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float xs[HC_MAX_STREAMS];
+    for (int d = threadIdx.x * V; d < D; d += blockDim.x * V) {
+        float xs[HC_MAX_STREAMS][V];
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s) xs[s] = s < S ? xt[(size_t)s * D + d] : 0.f;
-        float u = 0.f;
+        for (int s = 0; s < HC_MAX_STREAMS; ++s) {
+            if (s < S) hc_load<V>(xt + (size_t)s * D + d, xs[s]);
+            else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) xs[s][e] = 0.f;
+            }
+        }
+        float u[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) u[e] = 0.f;
         if (y) {
-            const float yv = to_f32(y[t * D + d]);
+            float yv[V];
+            hc_load<V>(y + t * D + d, yv);
 #pragma unroll
             for (int to = 0; to < HC_MAX_STREAMS; ++to) {
                 if (to >= S) break;
-                float acc = 0.f;
+                float acc[V];
+#pragma unroll
+                for (int e = 0; e < V; ++e) acc[e] = 0.f;
 #pragma unroll
                 for (int s = 0; s < HC_MAX_STREAMS; ++s)
-                    if (s < S) acc = fmaf(s_mix[s * S + to], xs[s], acc);
-                acc = fmaf(s_out[to], yv, acc);
-                if (!rows) xt[(size_t)to * D + d] = acc;
-                u = fmaf(s_in[to], acc, u);
+                    if (s < S) {
+                        const float w = s_mix[s * S + to];
+#pragma unroll
+                        for (int e = 0; e < V; ++e) acc[e] = fmaf(w, xs[s][e], acc[e]);
+                    }
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    acc[e] = fmaf(s_out[to], yv[e], acc[e]);
+                    u[e] = fmaf(s_in[to], acc[e], u[e]);
+                }
+                if (!rows) hc_store<V>(xt + (size_t)to * D + d, acc);
             }
         } else {
 #pragma unroll
             for (int s = 0; s < HC_MAX_STREAMS; ++s)
-                if (s < S) u = fmaf(s_in[s], xs[s], u);
+                if (s < S) {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) u[e] = fmaf(s_in[s], xs[s][e], u[e]);
+                }
         }
-        hu[d] = u;
-        ss += u * u;
+        hc_store<V>(hu + d, u);
+#pragma unroll
+        for (int e = 0; e < V; ++e) ss += u[e] * u[e];
     }
+    // every thread reads back the coordinates it wrote itself: no barrier is needed before these loops
     if (sum_out)
-        for (int d = threadIdx.x; d < D; d += blockDim.x) sum_out[(size_t)r * D + d] = hu[d];
+        for (int d = threadIdx.x * V; d < D; d += blockDim.x * V) {
+            float u[V];
+            hc_load<V>(hu + d, u);
+            hc_store<V>(sum_out + (size_t)r * D + d, u);
+        }
     if (!h) return;
-    if (!norm_w) {
-        for (int d = threadIdx.x; d < D; d += blockDim.x) h[(size_t)r * D + d] = from_f32<TA>(hu[d]);
-        return;
+    float inv = 1.0f;
+    if (norm_w) inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)D + eps);
+    for (int d = threadIdx.x * V; d < D; d += blockDim.x * V) {
+        float u[V], w[V];
+        hc_load<V>(hu + d, u);
+        if (norm_w) {
+            hc_load<V>(norm_w + d, w);
+#pragma unroll
+            for (int e = 0; e < V; ++e) u[e] = u[e] * inv * w[e];
+        }
+        hc_store<V>(h + (size_t)r * D + d, u);
     }
-    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)D + eps);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) h[(size_t)r * D + d] = from_f32<TA>(hu[d] * inv * norm_w[d]);
 }
 
 // x float32 [T, S, D] (updated in place unless rows is given); y [T, D] in the activation type or nullptr (nothing pending);
@@ -81,16 +149,21 @@ PICO_API int pico_hyper_step(float* x, const void* y, const float* mix, const fl
     if (S < 1 || S > HC_MAX_STREAMS || D < 1 || (size_t)D * sizeof(float) > 160 * 1024) return PICO_ERR_SIZE;
     if (y && (!mix || !outw)) return PICO_ERR_SIZE;
     const size_t smem = (size_t)D * sizeof(float);
-#define HC_LAUNCH(TA)                                                                                                   \
+#define HC_LAUNCH_V(TA, V)                                                                                              \
     do {                                                                                                                \
         if (smem > 48 * 1024)                                                                                           \
-            cudaFuncSetAttribute(hyper_step_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        pico_launch((hyper_step_kernel<TA>), dim3(R), dim3(256), smem, stream, x, (const TA*)y, mix, outw, inw, norm_w, eps, \
+            cudaFuncSetAttribute(hyper_step_kernel<TA, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        pico_launch((hyper_step_kernel<TA, V>), dim3(R), dim3(256), smem, stream, x, (const TA*)y, mix, outw, inw, norm_w, eps, \
                     (TA*)h, rows, sum_out, S, D);                                                                       \
     } while (0)
+    // 16-byte accesses when every row starts on such a boundary (8 bytes for bfloat16 rows)
+    const bool vec = D % 4 == 0 && ((uintptr_t)x | (uintptr_t)norm_w | (uintptr_t)sum_out) % 16 == 0 &&
+                     ((uintptr_t)y | (uintptr_t)h) % 16 == 0;
+#define HC_LAUNCH(TA) do { if (vec) HC_LAUNCH_V(TA, 4); else HC_LAUNCH_V(TA, 1); } while (0)
     if (dtype == PICO_F32) HC_LAUNCH(float);
     else if (dtype == PICO_BF16) HC_LAUNCH(bf16);
     else return PICO_ERR_DTYPE;
+#undef HC_LAUNCH_V
 #undef HC_LAUNCH
     return pico_launch_status();
 }

@@ -184,13 +184,23 @@ gated_linear_scan_kernel(float* __restrict__ state, const int* __restrict__ seg_
     const int i = e % d;
     const size_t base = (size_t)gl_chunk_base(cu_q, seg, chunk);
     float* sp = state + ((size_t)seg_slots[seg] * H + h) * (size_t)per_head + e;
+    float* cs = chunk_state + (base * H + h) * (size_t)per_head + e;
+    const float* cg = chunk_gate + (base * H + h) * (size_t)d + i;
+    const size_t step = (size_t)H * per_head, gstep = (size_t)H * d;
     float S = *sp;
-    for (int c = 0; c < n_chunks; ++c) {
-        const size_t ci = (base + c) * H + h;
-        float* cs = chunk_state + ci * (size_t)per_head + e;
-        const float local = *cs;
-        *cs = S;
-        S = fmaf(chunk_gate[ci * d + i], S, local);
+    for (int c0 = 0; c0 < n_chunks; c0 += 8) {          // the loads of eight chunks are in flight together
+        float local[8], g[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            local[k] = c0 + k < n_chunks ? cs[(size_t)(c0 + k) * step] : 0.f;
+            g[k] = c0 + k < n_chunks ? cg[(size_t)(c0 + k) * gstep] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (c0 + k < n_chunks) {
+                cs[(size_t)(c0 + k) * step] = S;
+                S = fmaf(g[k], S, local[k]);
+            }
     }
     *sp = S;
 }
