@@ -41,7 +41,9 @@ __device__ __forceinline__ int gl_chunk_base(const int* __restrict__ cu_q, int s
     return base;
 }
 
-template <int DPL, int GATE, bool STATE_ONLY>
+// XCOL (GATE 1; dv = 64 n + 1, as when a column of ones rides with the values): the blocks cover the first dv - 1 columns
+// and the first warp of the first block carries the last one as a ninth column, instead of a block for one column.
+template <int DPL, int GATE, bool STATE_ONLY, bool XCOL>
 __global__ void __launch_bounds__(GL_WARPS * 32)
 gated_linear_attention_kernel(const float* __restrict__ q, int q_stride, const float* __restrict__ k, int k_stride,
                               const float* __restrict__ v, int v_stride, const float* __restrict__ gate, int gate_stride,
@@ -85,28 +87,77 @@ gated_linear_attention_kernel(const float* __restrict__ q, int q_stride, const f
     }
     float* mypart = part + (size_t)warp * GL_TOK * 32 * GL_COLS;
     const bool live = col0 < dv;                       // uniform for the warp
+    const bool xcol = XCOL && blockIdx.x == 0 && warp == 0;
+    const int jx = dv - 1;                             // the ninth column
+    float* vxs = as + GL_TOK;                          // [GL_TOK] its values (GATE 1 leaves the room)
+    float Sx[DPL];
+#pragma unroll
+    for (int r = 0; r < DPL; ++r) {
+        const int i = lane + 32 * r;
+        Sx[r] = (xcol && !STATE_ONLY && i < d) ? st[(size_t)jx * d + i] : 0.f;
+    }
+    // Each thread's share of eight tokens' q, k, gates and values: asked for while the eight tokens before are walked, kept
+    // in registers, put into shared memory at the top of the next round.
+    constexpr int NTH = GL_WARPS * 32;
+    static_assert(GL_TOK * GL_WARPS * GL_COLS == 2 * NTH, "two values a thread and round");
+    int pf_tt[DPL], pf_i[DPL];                         // token of the round (>= GL_TOK: none) and row of element j
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+        const int idx = threadIdx.x + j * NTH;
+        pf_tt[j] = idx / d;
+        pf_i[j] = idx - pf_tt[j] * d;
+    }
+    const int v_tt = threadIdx.x / (GL_WARPS * GL_COLS), v_c = threadIdx.x % (GL_WARPS * GL_COLS);
+    const bool v_in = col_base + v_c < dv;
+    float rq[DPL], rk[DPL], ra[DPL], rv[2] = {0.f, 0.f}, ra1 = 0.f, rvx = 0.f;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) rq[j] = rk[j] = ra[j] = 0.f;
+    auto fetch = [&](int t0, int nt) {
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) {
+            if (pf_tt[j] < nt) {
+                const size_t t = (size_t)(t0 + pf_tt[j]);
+                if (!STATE_ONLY) rq[j] = q[t * q_stride + hq * d + pf_i[j]];
+                rk[j] = k[t * k_stride + hq * d + pf_i[j]];
+                if (GATE == 2) ra[j] = gate[t * gate_stride + (size_t)h * d + pf_i[j]];
+            }
+        }
+        if (GATE == 1 && threadIdx.x < nt) ra1 = gate[(size_t)(t0 + threadIdx.x) * gate_stride + h];
+        if (XCOL && blockIdx.x == 0 && threadIdx.x >= 32 && threadIdx.x < 32 + nt)
+            rvx = v[(size_t)(t0 + threadIdx.x - 32) * v_stride + (size_t)h * dv + jx];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int tt = v_tt + j * (GL_TOK / 2);
+            rv[j] = (tt < nt && v_in) ? v[(size_t)(t0 + tt) * v_stride + (size_t)h * dv + col_base + v_c] : 0.f;
+        }
+    };
+    fetch(t_begin, min(GL_TOK, t_end - t_begin));
     for (int t0 = t_begin; t0 < t_end; t0 += GL_TOK) {
         const int nt = min(GL_TOK, t_end - t0);
         __syncthreads();                               // everyone is done with the tokens before
-        for (int idx = threadIdx.x; idx < nt * d; idx += GL_WARPS * 32) {
-            const int tt = idx / d, i = idx - tt * d;
-            const size_t t = (size_t)(t0 + tt);
-            if (!STATE_ONLY) qs[tt * dp + i] = q[t * q_stride + hq * d + i];
-            ks[tt * dp + i] = k[t * k_stride + hq * d + i];
-            if (GATE == 2) as[tt * dp + i] = gate[t * gate_stride + (size_t)h * d + i];
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) {
+            if (pf_tt[j] < nt) {
+                if (!STATE_ONLY) qs[pf_tt[j] * dp + pf_i[j]] = rq[j];
+                ks[pf_tt[j] * dp + pf_i[j]] = rk[j];
+                if (GATE == 2) as[pf_tt[j] * dp + pf_i[j]] = ra[j];
+            }
         }
-        if (GATE == 1 && threadIdx.x < nt) as[threadIdx.x] = gate[(size_t)(t0 + threadIdx.x) * gate_stride + h];
-        for (int idx = threadIdx.x; idx < nt * GL_WARPS * GL_COLS; idx += GL_WARPS * 32) {
-            const int tt = idx / (GL_WARPS * GL_COLS), j = col_base + idx % (GL_WARPS * GL_COLS);
-            vs[idx] = j < dv ? v[(size_t)(t0 + tt) * v_stride + (size_t)h * dv + j] : 0.f;
+        if (GATE == 1 && threadIdx.x < nt) as[threadIdx.x] = ra1;
+        if (XCOL && blockIdx.x == 0 && threadIdx.x >= 32 && threadIdx.x < 32 + nt) vxs[threadIdx.x - 32] = rvx;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int tt = v_tt + j * (GL_TOK / 2);
+            if (tt < nt) vs[tt * (GL_WARPS * GL_COLS) + v_c] = rv[j];
         }
         __syncthreads();
+        if (t0 + GL_TOK < t_end) fetch(t0 + GL_TOK, min(GL_TOK, t_end - t0 - GL_TOK));
         if (!live) continue;                           // a warp past the last column only helps to load
         for (int tt = 0; tt < nt; ++tt) {
             const float4 va = *reinterpret_cast<const float4*>(vs + tt * GL_WARPS * GL_COLS + warp * GL_COLS);
             const float4 vb = *reinterpret_cast<const float4*>(vs + tt * GL_WARPS * GL_COLS + warp * GL_COLS + 4);
             const float vv[GL_COLS] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-            float p[GL_COLS];
+            float p[GL_COLS], px = 0.f;
 #pragma unroll
             for (int c = 0; c < GL_COLS; ++c) p[c] = 0.f;
             const float a1 = GATE == 1 ? as[tt] : 1.0f;
@@ -123,6 +174,14 @@ gated_linear_attention_kernel(const float* __restrict__ q, int q_stride, const f
                     S[r][c] = fmaf(a, S[r][c], kk * vv[c]);
                     if (!STATE_ONLY) p[c] = fmaf(S[r][c], qq, p[c]);
                 }
+                if (XCOL && xcol) {
+                    Sx[r] = fmaf(a, Sx[r], kk * vxs[tt]);
+                    if (!STATE_ONLY) px = fmaf(Sx[r], qq, px);
+                }
+            }
+            if (XCOL && xcol && !STATE_ONLY) {
+                px = warp_sum(px);
+                if (lane == 0) out[(size_t)(t0 + tt) * out_stride + (size_t)h * dv + jx] = px;
             }
             if (!STATE_ONLY) {
                 float* dst = mypart + ((size_t)tt * 32 + lane) * GL_COLS;
@@ -158,6 +217,13 @@ gated_linear_attention_kernel(const float* __restrict__ q, int q_stride, const f
                 const int i = lane + 32 * r, j = col0 + c;
                 if (i < d && j < dv) st[(size_t)j * d + i] = S[r][c];
             }
+        if (XCOL && xcol) {
+#pragma unroll
+            for (int r = 0; r < DPL; ++r) {
+                const int i = lane + 32 * r;
+                if (i < d) st[(size_t)jx * d + i] = Sx[r];
+            }
+        }
     }
     if (STATE_ONLY && blockIdx.x == 0 && warp == 0) {
 #pragma unroll
@@ -223,19 +289,22 @@ PICO_API int pico_gated_linear_attention(const float* q, int q_stride, const flo
     const int dpl = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8;
     const int dp = (d + 3) & ~3;
     const size_t smem = ((size_t)3 * GL_TOK * dp + GL_TOK * GL_WARPS * GL_COLS + (size_t)GL_WARPS * GL_TOK * 32 * GL_COLS) * sizeof(float);
-    const dim3 grid((dv + GL_WARPS * GL_COLS - 1) / (GL_WARPS * GL_COLS), H, S * max_chunks);
-#define GL_LAUNCH(DPL, G, SO)                                                                                            \
+    const bool xc = gate_kind == 1 && dv > 1 && dv % (GL_WARPS * GL_COLS) == 1;      // the last column rides with a warp
+    const dim3 grid(xc ? dv / (GL_WARPS * GL_COLS) : (dv + GL_WARPS * GL_COLS - 1) / (GL_WARPS * GL_COLS), H, S * max_chunks);
+#define GL_LAUNCH(DPL, G, SO, XC)                                                                                        \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
-            cudaFuncSetAttribute(gated_linear_attention_kernel<DPL, G, SO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+            cudaFuncSetAttribute(gated_linear_attention_kernel<DPL, G, SO, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)smem);                                                                             \
-        pico_launch((gated_linear_attention_kernel<DPL, G, SO>), grid, dim3(GL_WARPS * 32), smem, stream, q, q_stride, k, \
+        pico_launch((gated_linear_attention_kernel<DPL, G, SO, XC>), grid, dim3(GL_WARPS * 32), smem, stream, q, q_stride, k, \
                     k_stride, v, v_stride, gate, gate_stride, state, seg_slots, cu_q, positions, out, out_stride, H, qk_rep, d, dv,   \
                     chunk, max_chunks, chunk_state, chunk_gate);                                                         \
     } while (0)
 #define GL_BY_GATE(DPL, SO)                                                                                              \
     do {                                                                                                                 \
-        if (gate_kind == 1) GL_LAUNCH(DPL, 1, SO); else GL_LAUNCH(DPL, 2, SO);                                           \
+        if (gate_kind == 2) GL_LAUNCH(DPL, 2, SO, false);                                                                \
+        else if (xc) GL_LAUNCH(DPL, 1, SO, true);                                                                        \
+        else GL_LAUNCH(DPL, 1, SO, false);                                                                               \
     } while (0)
 #define GL_BY_DPL(SO)                                                                                                    \
     do {                                                                                                                 \
@@ -255,25 +324,28 @@ PICO_API int pico_gated_linear_attention(const float* q, int q_stride, const flo
 }
 
 // ------------------------------------------------------------------------------------------ exponential gates
-// A warp per (head, segment): the running maximum m_t = max(f_t + m_(t-1), i_t) is a scan under the composition of the maps
-// x -> max(x + a, b), 32 tokens a round.  i = cap tanh((z_i + b_i) / cap), f = logsigmoid(cap tanh((z_f + b_f) / cap)).
+// A block of one to eight warps per (head, segment): the running maximum m_t = max(f_t + m_(t-1), i_t) is a scan under the
+// composition of the maps x -> max(x + a, b): inside a warp by shuffles, across the warps through shared memory, 32
+// tokens a warp and round.  i = cap tanh((z_i + b_i) / cap), f = logsigmoid(cap tanh((z_f + b_f) / cap)).
 // Writes, per token and head: keep = exp(f + m_(t-1) - m_t), put = exp(i - m_t), floor = exp(-m_t); m [slots, H] goes on.
+#define MG_WARPS 8
 template <typename TA>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(MG_WARPS * 32)
 mlstm_gates_kernel(const TA* __restrict__ proj, int row_stride, int i_off, int f_off, const float* __restrict__ i_bias,
                    const float* __restrict__ f_bias, float cap, float* __restrict__ m_state, const int* __restrict__ seg_slots,
                    const int* __restrict__ cu_q, const int* __restrict__ positions, float* __restrict__ keep,
                    float* __restrict__ put, float* __restrict__ floor_, int H) {
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.x, seg = blockIdx.y, lane = threadIdx.x;
+    __shared__ float sA[MG_WARPS], sB[MG_WARPS];
+    const int h = blockIdx.x, seg = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int t_begin = cu_q[seg], t_end = cu_q[seg + 1];
     if (t_end <= t_begin || positions[t_begin] < 0) return;
     float* mp = m_state + (size_t)seg_slots[seg] * H + h;
-    float m = *mp;
+    float m = *mp;                                    // every thread follows the block's m
     const float bi = i_bias ? i_bias[h] : 0.f, bf = f_bias ? f_bias[h] : 0.f;
-    for (int t0 = t_begin; t0 < t_end; t0 += 32) {
-        const int t = t0 + lane;
+    for (int t0 = t_begin; t0 < t_end; t0 += nw * 32) {
+        const int t = t0 + (int)threadIdx.x;
         const bool valid = t < t_end;
         float a = 0.f, b = -INFINITY;                 // the identity map
         if (valid) {
@@ -282,7 +354,7 @@ mlstm_gates_kernel(const TA* __restrict__ proj, int row_stride, int i_off, int f
             b = cap * tanhf(zi / cap);
             a = rc_logsigmoid(cap * tanhf(zf / cap));
         }
-        float A = a, B = b;
+        float A = a, B = b;                           // the map of this warp's tokens up to and with this one
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const float A0 = __shfl_up_sync(0xffffffffu, A, o), B0 = __shfl_up_sync(0xffffffffu, B, o);
@@ -291,18 +363,26 @@ mlstm_gates_kernel(const TA* __restrict__ proj, int row_stride, int i_off, int f
                 A = A0 + A;
             }
         }
-        const float mt = fmaxf(m + A, B);
+        if (lane == 31) {
+            sA[warp] = A;
+            sB[warp] = B;
+        }
+        __syncthreads();
+        float m_in = m;                               // m before this warp's first token
+        for (int w = 0; w < warp; ++w) m_in = fmaxf(m_in + sA[w], sB[w]);
+        const float mt = fmaxf(m_in + A, B);
         float mprev = __shfl_up_sync(0xffffffffu, mt, 1);
-        if (lane == 0) mprev = m;
+        if (lane == 0) mprev = m_in;
         if (valid) {
             const size_t o = (size_t)t * H + h;
             keep[o] = expf(a + mprev - mt);
             put[o] = expf(b - mt);
             floor_[o] = expf(-mt);
         }
-        m = __shfl_sync(0xffffffffu, mt, min(31, t_end - t0 - 1));
+        for (int w = 0; w < nw; ++w) m = fmaxf(m + sA[w], sB[w]);            // tokens past the end are identity maps
+        __syncthreads();                              // sA and sB are written again in the next round
     }
-    if (lane == 0) *mp = m;
+    if (threadIdx.x == 0) *mp = m;
 }
 
 // prepared row of a token: [q: H d | k: H d | v: H (dv + 1)] float32, with q * q_scale, k * put[t, h], v and a last column 1.
@@ -312,19 +392,22 @@ __global__ void mlstm_prepare_kernel(const TA* __restrict__ proj, int row_stride
                                      float* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
+    // gridDim.y blocks per token (several when the step is short; blocks stride over the tokens): 32-bit index arithmetic
+    // inside the row
     const int nqk = H * d, nv = H * (dv + 1), n = 2 * nqk + nv;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / n;
-        const int c = (int)(idx - t * n);
+    const size_t T = total / n;
+    for (size_t t = blockIdx.x; t < T; t += gridDim.x) {
         const TA* row = proj + t * row_stride;
-        float val;
-        if (c < nqk) val = to_f32(row[q_off + c]) * q_scale;
-        else if (c < 2 * nqk) val = to_f32(row[k_off + c - nqk]) * put[t * H + (c - nqk) / d];
-        else {
-            const int hv = (c - 2 * nqk) / (dv + 1), j = (c - 2 * nqk) - hv * (dv + 1);
-            val = j < dv ? to_f32(row[v_off + hv * dv + j]) : 1.0f;
+        float* o = out + t * n;
+        const int c0 = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;
+        for (int c = c0; c < nqk; c += step) {
+            o[c] = to_f32(row[q_off + c]) * q_scale;
+            o[nqk + c] = to_f32(row[k_off + c]) * put[t * H + c / d];
         }
-        out[idx] = val;
+        for (int c = c0; c < nv; c += step) {
+            const int hv = c / (dv + 1), j = c - hv * (dv + 1);
+            o[2 * nqk + c] = j < dv ? to_f32(row[v_off + hv * dv + j]) : 1.0f;
+        }
     }
 }
 
@@ -337,13 +420,14 @@ PICO_API int pico_mlstm_prepare(const void* proj, int row_stride, int q_off, int
     if (H < 1 || H > 65535 || S > 65535 || d < 1 || dv < 1 || !(cap > 0.f)) return PICO_ERR_SIZE;
     const size_t total = (size_t)T * ((size_t)2 * H * d + (size_t)H * (dv + 1));
     const long long capb = 16LL * pico_num_sms();
-    const size_t want = (total + 255) / 256;
-    const int blocks = (int)((long long)want > capb ? capb : (long long)want);
+    const int blocks = (int)((long long)T > capb ? capb : (long long)T);
+    const int per_seg = (T + S - 1) / S;              // single tokens: a warp; long portions: eight
+    const int gate_threads = per_seg <= 32 ? 32 : per_seg <= 128 ? 128 : MG_WARPS * 32;
 #define ML_LAUNCH(TA)                                                                                                   \
     do {                                                                                                                \
-        pico_launch((mlstm_gates_kernel<TA>), dim3(H, S), dim3(32), 0, stream, (const TA*)proj, row_stride, i_off, f_off, \
+        pico_launch((mlstm_gates_kernel<TA>), dim3(H, S), dim3(gate_threads), 0, stream, (const TA*)proj, row_stride, i_off, f_off, \
                     i_bias, f_bias, cap, m_state, seg_slots, cu_q, positions, keep, put, floor_, H);                    \
-        pico_launch((mlstm_prepare_kernel<TA>), dim3(blocks), dim3(256), 0, stream, (const TA*)proj, row_stride, q_off, k_off, \
+        pico_launch((mlstm_prepare_kernel<TA>), dim3(blocks, T < 512 ? 8 : 1), dim3(256), 0, stream, (const TA*)proj, row_stride, q_off, k_off, \
                     v_off, (const float*)put, q_scale, H, d, dv, total, prepared);                                      \
     } while (0)
     if (dtype == PICO_F32) ML_LAUNCH(float);
@@ -403,27 +487,55 @@ PICO_API int pico_hgrn2_prepare(const void* proj, int row_stride, int q_off, int
 // the segment's first token come from the request's state [slots, taps - 1, C] (its last taps - 1 inputs, oldest first; zero
 // at a request's start).  conv_state_kernel, launched after, leaves the segment's last taps - 1 inputs there.
 #define CONV_MAX_TAPS 16
-template <typename TA>
-__global__ void causal_conv_silu_kernel(const TA* __restrict__ proj, int row_stride, int c_off, const float* __restrict__ w,
-                                        const float* __restrict__ b, const float* __restrict__ conv_state,
-                                        const int* __restrict__ tok_seg, const int* __restrict__ seg_slots,
-                                        const int* __restrict__ cu_q, const int* __restrict__ positions, int C, int taps,
-                                        size_t total, float* __restrict__ out) {
+#define CV_TOK 8
+template <typename TA, int M>      // M: the taps the registers hold (4 or CONV_MAX_TAPS)
+__global__ void __launch_bounds__(256)
+causal_conv_silu_kernel(const TA* __restrict__ proj, int row_stride, int c_off, const float* __restrict__ w,
+                        const float* __restrict__ b, const float* __restrict__ conv_state, const int* __restrict__ tok_seg,
+                        const int* __restrict__ seg_slots, const int* __restrict__ cu_q, const int* __restrict__ positions,
+                        int C, int taps, int T, int tpb, float* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int t = (int)(idx / C), c = (int)(idx - (size_t)t * C);
-        if (positions[t] < 0) { out[idx] = 0.f; continue; }
-        const int seg = tok_seg[t], begin = cu_q[seg];
-        const float* st = conv_state + (size_t)seg_slots[seg] * (taps - 1) * C;
-        float acc = b ? b[c] : 0.f;
-        for (int j = 0; j < taps; ++j) {
-            const int src = t - (taps - 1) + j;
-            const float x = src >= begin ? to_f32(proj[(size_t)src * row_stride + c_off + c])
-                                         : st[(size_t)(taps - 1 + src - begin) * C + c];
-            acc = fmaf(w[(size_t)c * taps + j], x, acc);
+    // a block takes tpb consecutive tokens (one when the step is short) of 256 channels, a thread one channel: it walks the
+    // tokens with the last inputs of its channel in registers (the newest at the right end, the weights likewise), so every input is read once
+    const int tb = blockIdx.x * tpb, te = min(T, tb + tpb);
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c < C) {
+        float wt[M], win[M];
+#pragma unroll
+        for (int k = 0; k < M; ++k) {
+            wt[M - 1 - k] = k < taps ? w[(size_t)c * taps + taps - 1 - k] : 0.f;
+            win[k] = 0.f;
         }
-        out[idx] = rc_silu(acc);
+        const float bias = b ? b[c] : 0.f;
+        bool have = false;
+        for (int t = tb; t < te; ++t) {
+            if (positions[t] < 0) {
+                out[(size_t)t * C + c] = 0.f;
+                have = false;
+                continue;
+            }
+            const int seg = tok_seg[t], begin = cu_q[seg];
+            if (!have || t == begin) {                 // the inputs before this token: of this step, or kept by the request
+                const float* st = conv_state + (size_t)seg_slots[seg] * (taps - 1) * C;
+#pragma unroll
+                for (int k = 1; k < M; ++k) {
+                    if (k < taps) {
+                        const int src = t - k;
+                        win[M - 1 - k] = src >= begin ? to_f32(proj[(size_t)src * row_stride + c_off + c])
+                                                      : st[(size_t)(taps - 1 + src - begin) * C + c];
+                    }
+                }
+                have = true;
+            }
+            win[M - 1] = to_f32(proj[(size_t)t * row_stride + c_off + c]);
+            float acc = bias;
+#pragma unroll
+            for (int k = 0; k < M; ++k) acc = fmaf(wt[k], win[k], acc);      // oldest first; unused taps weigh zero
+            out[(size_t)t * C + c] = rc_silu(acc);
+#pragma unroll
+            for (int k = 0; k < M - 1; ++k) win[k] = win[k + 1];
+        }
     }
 }
 
@@ -453,15 +565,17 @@ PICO_API int pico_causal_conv_silu(const void* proj, int row_stride, int c_off, 
                                    const int* positions, float* out, int T, int S, int C, int taps, int dtype,
                                    cudaStream_t stream) {
     if (T <= 0 || S <= 0) return 0;
-    if (C < 1 || taps < 1 || taps > CONV_MAX_TAPS || S > 65535) return PICO_ERR_SIZE;
-    const size_t total = (size_t)T * C;
-    const long long capb = 16LL * pico_num_sms();
-    const size_t want = (total + 255) / 256;
-    const int blocks = (int)((long long)want > capb ? capb : (long long)want);
+    if (C < 1 || taps < 1 || taps > CONV_MAX_TAPS || S > 65535 || (C + 255) / 256 > 65535) return PICO_ERR_SIZE;
+    const int tpb = T >= 32 * CV_TOK ? CV_TOK : 1;
+    const int blocks = (T + tpb - 1) / tpb;
 #define CV_LAUNCH(TA)                                                                                                    \
     do {                                                                                                                 \
-        pico_launch((causal_conv_silu_kernel<TA>), dim3(blocks), dim3(256), 0, stream, (const TA*)proj, row_stride, c_off, w, b, \
-                    (const float*)conv_state, tok_seg, seg_slots, cu_q, positions, C, taps, total, out);                 \
+        if (taps <= 4)                                                                                                   \
+            pico_launch((causal_conv_silu_kernel<TA, 4>), dim3(blocks, (C + 255) / 256), dim3(256), 0, stream, (const TA*)proj,  \
+                        row_stride, c_off, w, b, (const float*)conv_state, tok_seg, seg_slots, cu_q, positions, C, taps, T, tpb, out); \
+        else                                                                                                             \
+            pico_launch((causal_conv_silu_kernel<TA, CONV_MAX_TAPS>), dim3(blocks, (C + 255) / 256), dim3(256), 0, stream, (const TA*)proj, \
+                        row_stride, c_off, w, b, (const float*)conv_state, tok_seg, seg_slots, cu_q, positions, C, taps, T, tpb, out); \
         if (taps > 1)                                                                                                    \
             pico_launch((conv_state_kernel<TA>), dim3((C + 127) / 128, S), dim3(128), 0, stream, (const TA*)proj, row_stride, \
                         c_off, conv_state, seg_slots, cu_q, positions, C, taps);                                         \
@@ -512,23 +626,27 @@ PICO_API int pico_mamba2_prepare(const void* proj, int row_stride, int dt_off, c
 }
 
 // ------------------------------------------------------------------------------------------ the norm that finishes them
-// A block per token, its warps take the groups in turn.  For column j of group g (col = g * n + j):
+// A warp per (token, group), four groups a block - or, for groups of 512 columns and more (WIDE), a block per (token,
+// group).  For column j of group g (col = g * n + j):
 //   val = x[t, g * group_stride + j]
 //   den_floor:  val /= max(|x[t, g * group_stride + n]|, den_floor[t, g]) + 1e-6      (the normaliser rides as column n)
 //   skip:       val += skip_w[col / skip_head] * skip[t, col]
 //   pre_gate:   val *= silu(pre_gate[t, col])
 //   y[t, col] = val / sqrt(mean_j val^2 + eps) * w[col] * sigmoid(post_gate[t, col])       (w, post_gate optional)
-template <typename TA>
-__global__ void __launch_bounds__(128)
+template <typename TA, bool WIDE>
+__global__ void __launch_bounds__(256)
 group_rms_norm_kernel(const float* __restrict__ x, int x_stride, int group_stride, int groups, int n, const float* __restrict__ w,
                       float eps, const float* __restrict__ den_floor, const float* __restrict__ skip, int skip_stride,
                       const float* __restrict__ skip_w, int skip_head, const TA* __restrict__ pre_gate, int pre_stride,
                       const TA* __restrict__ post_gate, int post_stride, TA* __restrict__ y) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float scratch[33];
     const size_t t = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int g = warp; g < groups; g += nw) {
+    const int g = WIDE ? blockIdx.y : blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int tid = WIDE ? threadIdx.x : threadIdx.x & 31, nth = WIDE ? blockDim.x : 32;
+    if (g >= groups) return;                           // whole warps only, and none in the WIDE form
+    {
         const float* xg = x + t * x_stride + (size_t)g * group_stride;
         float inv_den = 1.0f;
         if (den_floor) inv_den = 1.0f / (fmaxf(fabsf(xg[n]), den_floor[t * groups + g]) + 1e-6f);
@@ -541,12 +659,12 @@ group_rms_norm_kernel(const float* __restrict__ x, int x_stride, int group_strid
             return val;
         };
         float ss = 0.f;
-        for (int j = lane; j < n; j += 32) {
+        for (int j = tid; j < n; j += nth) {
             const float val = value(j);
             ss += val * val;
         }
-        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
-        for (int j = lane; j < n; j += 32) {
+        const float inv = 1.0f / sqrtf((WIDE ? block_sum(ss, scratch) : warp_sum(ss)) / (float)n + eps);
+        for (int j = tid; j < n; j += nth) {
             const int col = g * n + j;
             float o = value(j) * inv * (w ? w[col] : 1.0f);
             if (post_gate) o *= rc_sigmoid(to_f32(post_gate[t * post_stride + col]));
@@ -561,15 +679,17 @@ PICO_API int pico_group_rms_norm(const float* x, int x_stride, int group_stride,
                                  int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (groups < 1 || n < 1 || (skip && (!skip_w || skip_head < 1))) return PICO_ERR_SIZE;
-    if (dtype == PICO_F32)
-        pico_launch((group_rms_norm_kernel<float>), dim3(T), dim3(128), 0, stream, x, x_stride, group_stride, groups, n, w, eps,
-                    den_floor, skip, skip_stride, skip_w, skip_head, (const float*)pre_gate, pre_stride, (const float*)post_gate,
-                    post_stride, (float*)y);
-    else if (dtype == PICO_BF16)
-        pico_launch((group_rms_norm_kernel<bf16>), dim3(T), dim3(128), 0, stream, x, x_stride, group_stride, groups, n, w, eps,
-                    den_floor, skip, skip_stride, skip_w, skip_head, (const bf16*)pre_gate, pre_stride, (const bf16*)post_gate,
-                    post_stride, (bf16*)y);
+    if (groups > 65535 * 4) return PICO_ERR_SIZE;
+    const bool wide = n >= 512;
+    const dim3 grid(T, wide ? groups : (groups + 3) / 4), block(wide ? 256 : 128);
+#define GN_LAUNCH(TA, W)                                                                                                 \
+    pico_launch((group_rms_norm_kernel<TA, W>), grid, block, 0, stream, x, x_stride, group_stride, groups, n, w, eps,     \
+                den_floor, skip, skip_stride, skip_w, skip_head, (const TA*)pre_gate, pre_stride, (const TA*)post_gate,  \
+                post_stride, (TA*)y)
+    if (dtype == PICO_F32) { if (wide) GN_LAUNCH(float, true); else GN_LAUNCH(float, false); }
+    else if (dtype == PICO_BF16) { if (wide) GN_LAUNCH(bf16, true); else GN_LAUNCH(bf16, false); }
     else
         return PICO_ERR_DTYPE;
+#undef GN_LAUNCH
     return pico_launch_status();
 }

@@ -370,7 +370,8 @@ def _close(got, want, dtype, what):
     assert err <= tol * max(1.0, float(want.abs().max())), f"{what}: {err}"
 
 
-@pytest.mark.parametrize("H,rep,d,dv", [(3, 1, 16, 24), (4, 2, 64, 16), (1, 1, 20, 13), (6, 3, 40, 70), (2, 1, 200, 33)])
+@pytest.mark.parametrize("H,rep,d,dv", [(3, 1, 16, 24), (4, 2, 64, 16), (1, 1, 20, 13), (6, 3, 40, 70), (2, 1, 200, 33), (2, 1, 24, 65),
+                                        (3, 1, 128, 129)])
 @pytest.mark.parametrize("per_row", [False, True])
 @pytest.mark.parametrize("chunk", [0, 16, 3])
 def test_gated_recurrence_kernel(H, rep, d, dv, per_row, chunk):
