@@ -73,8 +73,8 @@ class DistanceBiasAttention(Part):
 
     def plan(self, shape: StepShape) -> AttentionPlan:
         splits = decode_splits(shape, self.n_kv_heads)
-        if self.chunk:                                           # no token reads more keys than a chunk holds
-            while splits > 1 and splits * 128 > self.chunk:
+        if self.chunk:                                           # no token reads more keys than a chunk holds: parts of
+            while splits > 1 and splits * 512 > self.chunk:      # 512 keys at least
                 splits //= 2
         scratch = ops.attention_scratch_floats(shape.num_tokens, self.n_heads, self.row, splits)
         return AttentionPlan(key=(splits, 0), scratch_floats=scratch, splits=splits, pair_min_keys=0)
