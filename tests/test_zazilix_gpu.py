@@ -644,8 +644,12 @@ def test_command_line_writes_a_model_folder_and_generates(tmp_path, capsys):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_replay_of_a_model_folder(tmp_path, dtype):
+@pytest.mark.parametrize("keep", ["all", "no attention", "attention only"])
+def test_trace_replay_of_a_model_folder(tmp_path, dtype, keep):
+    """Also models that need no pages at all (no layer with attention) and models whose every layer has both pages and states."""
     raw = _raw("c", dtype)
+    if keep != "all":
+        raw["layers"] = [l for l in raw["layers"] if (l["type"] == "parallel") == (keep == "attention only")]
     tensors = _tensors(raw, SEEDS["c"])
     reqs = {f"r{i}": helpers.random_ids(n, raw["vocab"], 300 + i) for i, n in enumerate([40, 7, 95, 33, 64])}
     steps = helpers.trace_mixed(reqs, max_live=4, seed=1)
@@ -656,7 +660,6 @@ def test_trace_replay_of_a_model_folder(tmp_path, dtype):
                        input=lines, capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-3000:]
     logits = _oracle(raw, tensors, reqs)
-    for i, w in enumerate(helpers.expected_logits(steps, reqs, logits)):
-        if w is not None:
-            got = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, raw["vocab"]))
-            helpers.assert_close_logits(got, w.float(), REL[dtype], f"step {i}")
+    got = [None if w is None else torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, raw["vocab"]))
+           for i, w in enumerate(helpers.expected_logits(steps, reqs, logits))]
+    _compare(steps, reqs, got, logits, dtype, f"replay ({keep})")
