@@ -540,7 +540,7 @@ def test_norm_store_and_biased_attention_kernels(dtype, H, G, d, dv, ps, chunk):
 @pytest.mark.gpu
 @pytest.mark.parametrize("H,G,d,ps,chunk,window", [(4, 2, 64, 16, 100, None), (8, 2, 128, 16, 192, None), (2, 1, 128, 64, 0, None),
                                                    (6, 2, 48, 8, 70, None), (16, 1, 32, 4, 33, 50), (4, 4, 80, 16, 128, None),
-                                                   (2, 2, 64, 32, 64, 40)])
+                                                   (2, 2, 64, 32, 64, 40), (2, 2, 64, 16, 20, None), (8, 2, 128, 8, 9, None)])
 def test_biased_attention_on_tensor_cores(H, G, d, ps, chunk, window):
     """The bfloat16 kernels: portions of prompts (with tensor maps over the pages where the head size has them) beside
     single tokens in one and in four parts, over pages in any order that hold NaN wherever nothing was stored.  Sinks
