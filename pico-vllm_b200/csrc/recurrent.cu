@@ -592,16 +592,23 @@ PICO_API int pico_causal_conv_silu(const void* proj, int row_stride, int c_off, 
 template <typename TA>
 __global__ void mamba2_prepare_kernel(const TA* __restrict__ proj, int row_stride, int dt_off, const float* __restrict__ dt_bias,
                                       const float* __restrict__ a_log, const float* __restrict__ x, int x_stride, int H, int dv,
-                                      size_t total, float* __restrict__ keep, float* __restrict__ vdt) {
+                                      int T, float* __restrict__ keep, float* __restrict__ vdt) {
     pdl_launch_dependents();
     pdl_wait();
+    // gridDim.y blocks per token (several when the step is short; blocks stride over the tokens): the step sizes of the
+    // token's heads once into shared memory, then the products
+    extern __shared__ float dts[];                     // [H]
     const int n = H * dv;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / n;
-        const int c = (int)(idx - t * n), h = c / dv;
-        const float dt = rc_softplus(to_f32(proj[t * row_stride + dt_off + h]) + (dt_bias ? dt_bias[h] : 0.f));
-        if (c == h * dv) keep[t * H + h] = expf(-expf(a_log[h]) * dt);
-        vdt[idx] = dt * x[t * x_stride + c];
+    for (size_t t = blockIdx.x; t < (size_t)T; t += gridDim.x) {
+        __syncthreads();                               // the token before is done with dts
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            const float dt = rc_softplus(to_f32(proj[t * row_stride + dt_off + h]) + (dt_bias ? dt_bias[h] : 0.f));
+            dts[h] = dt;
+            if (blockIdx.y == 0) keep[t * H + h] = expf(-expf(a_log[h]) * dt);
+        }
+        __syncthreads();
+        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x)
+            vdt[t * n + c] = dts[c / dv] * x[t * x_stride + c];
     }
 }
 
@@ -609,17 +616,16 @@ PICO_API int pico_mamba2_prepare(const void* proj, int row_stride, int dt_off, c
                                  const float* x, int x_stride, float* keep, float* vdt, int T, int H, int dv, int dtype,
                                  cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (H < 1 || dv < 1) return PICO_ERR_SIZE;
-    const size_t total = (size_t)T * H * dv;
+    if (H < 1 || H > 8192 || dv < 1) return PICO_ERR_SIZE;
     const long long capb = 16LL * pico_num_sms();
-    const size_t want = (total + 255) / 256;
-    const int blocks = (int)((long long)want > capb ? capb : (long long)want);
+    const dim3 grid((int)((long long)T > capb ? capb : (long long)T), T < 512 ? 4 : 1);
+    const size_t smem = (size_t)H * sizeof(float);
     if (dtype == PICO_F32)
-        pico_launch((mamba2_prepare_kernel<float>), dim3(blocks), dim3(256), 0, stream, (const float*)proj, row_stride, dt_off,
-                    dt_bias, a_log, x, x_stride, H, dv, total, keep, vdt);
+        pico_launch((mamba2_prepare_kernel<float>), grid, dim3(256), smem, stream, (const float*)proj, row_stride, dt_off,
+                    dt_bias, a_log, x, x_stride, H, dv, T, keep, vdt);
     else if (dtype == PICO_BF16)
-        pico_launch((mamba2_prepare_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, (const bf16*)proj, row_stride, dt_off,
-                    dt_bias, a_log, x, x_stride, H, dv, total, keep, vdt);
+        pico_launch((mamba2_prepare_kernel<bf16>), grid, dim3(256), smem, stream, (const bf16*)proj, row_stride, dt_off,
+                    dt_bias, a_log, x, x_stride, H, dv, T, keep, vdt);
     else
         return PICO_ERR_DTYPE;
     return pico_launch_status();
