@@ -1,0 +1,250 @@
+// The gated delta rule: a matrix memory per head and request whose rows decay and whose write is corrected by what the
+// memory already holds under the key,
+//
+//   S <- diag(a_t) S ;   u = beta_t (v_t - S^T k_t) ;   S <- S + k_t u^T ;   o_t = S^T q_t          (S: [d, dv], float32)
+//
+// token by token, the read seeing the write.  With the decayed memory S' = diag(a_t) S both sums over rows are taken in one
+// pass,  r1 = S'^T k_t  and  r2 = S'^T q_t :  u = beta_t (v_t - r1),  o_t = r2 + u (k_t . q_t),  so a token costs one pass
+// over the registers, one reduction and one update.
+//
+// delta_prepare_kernel makes the float32 inputs of the recurrence from the projections: q and k as unit vectors per head
+// (q times d^-1/2), beta = sigmoid, the decay a = exp(-exp(A_log) softplus(z + bias)) per head and row, and k . q.
+// gated_delta_rule_kernel is the recurrence: the columns of S evolve independently of each other, so a block takes
+// DR_WARPS * 4 columns of one head of one segment, a warp four of them, a lane the rows lane, lane + 32, ... in registers;
+// the state is stored transposed [slot, head, dv, d].  A token's q, k and decay pass through shared memory, DR_TOK tokens a
+// round, the next round's loads in flight (cp.async) while this one is walked.  A segment of one token is a decode step; a
+// portion of a prompt goes on from the state the portion before left.
+//
+// Everything here is float32 whatever the activation type; only the projections read are not.
+#include "common.cuh"
+
+#define DR_TOK 8
+#define DR_WARPS 4
+#define DR_COLS 4
+
+__device__ __forceinline__ float dr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float dr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// One block per token.  xc float32 [T, >= q_off.. ] holds the convolved q and k (G heads of d each); proj (activation
+// type) holds one beta logit per head at b_off; dt [T, H * d] (activation type) the decay's argument before its bias.
+// prep float32 [T, P] with P = 2 G d + H d + H + G:  q | k | a | beta | k . q.
+template <typename TA>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const float* __restrict__ xc, int xc_stride, int q_off, int k_off, const TA* __restrict__ proj,
+                     int proj_stride, int b_off, const TA* __restrict__ dt, int dt_stride, const float* __restrict__ dt_bias,
+                     const float* __restrict__ a_log, float* __restrict__ prep, int P, int H, int G, int d, float q_scale,
+                     float unit_eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float* out = prep + t * P;
+    const float* row = xc + t * xc_stride;
+    for (int g = warp; g < G; g += nw) {
+        float sq = 0.f, sk = 0.f;
+        for (int i = lane; i < d; i += 32) {
+            const float a = row[q_off + g * d + i], b = row[k_off + g * d + i];
+            sq += a * a;
+            sk += b * b;
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        const float iq = q_scale / sqrtf(sq + unit_eps), ik = 1.0f / sqrtf(sk + unit_eps);
+        float kq = 0.f;
+        for (int i = lane; i < d; i += 32) {
+            const float a = row[q_off + g * d + i] * iq, b = row[k_off + g * d + i] * ik;
+            out[g * d + i] = a;
+            out[G * d + g * d + i] = b;
+            kq += a * b;
+        }
+        kq = warp_sum(kq);
+        if (lane == 0) out[2 * G * d + H * d + H + g] = kq;
+    }
+    for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+        const int h = i / d;
+        const float z = to_f32(dt[t * dt_stride + i]) + (dt_bias ? dt_bias[i] : 0.f);
+        out[2 * G * d + i] = expf(-expf(a_log[h]) * dr_softplus(z));
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        out[2 * G * d + H * d + h] = dr_sigmoid(to_f32(proj[t * proj_stride + b_off + h]));
+}
+
+PICO_API int pico_delta_prepare(const float* xc, int xc_stride, int q_off, int k_off, const void* proj, int proj_stride,
+                                int b_off, const void* dt, int dt_stride, const float* dt_bias, const float* a_log,
+                                float* prep, int T, int H, int G, int d, float q_scale, float unit_eps, int dtype,
+                                cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H < 1 || G < 1 || H % G || d < 1) return PICO_ERR_SIZE;
+    const int P = 2 * G * d + H * d + H + G;
+    if (dtype == PICO_F32)
+        pico_launch((delta_prepare_kernel<float>), dim3(T), dim3(128), 0, stream, xc, xc_stride, q_off, k_off,
+                    (const float*)proj, proj_stride, b_off, (const float*)dt, dt_stride, dt_bias, a_log, prep, P, H, G, d,
+                    q_scale, unit_eps);
+    else if (dtype == PICO_BF16)
+        pico_launch((delta_prepare_kernel<bf16>), dim3(T), dim3(128), 0, stream, xc, xc_stride, q_off, k_off,
+                    (const bf16*)proj, proj_stride, b_off, (const bf16*)dt, dt_stride, dt_bias, a_log, prep, P, H, G, d,
+                    q_scale, unit_eps);
+    else
+        return PICO_ERR_DTYPE;
+    return pico_launch_status();
+}
+
+__device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void dr_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+// prep: the rows delta_prepare_kernel wrote (q at 0, k at G d, a at 2 G d, beta and k . q after them); v float32 rows with
+// head h's values at h * dv; state float32 [slots, H, dv, d]; out float32 [T, H * dv].  Grid (column tiles, H, segments).
+template <int DPL>
+__global__ void __launch_bounds__(DR_WARPS * 32)
+gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __restrict__ v, int v_stride,
+                        float* __restrict__ state, const int* __restrict__ seg_slots, const int* __restrict__ cu_q,
+                        const int* __restrict__ positions, float* __restrict__ out, int out_stride, int H, int G, int d,
+                        int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float dsm[];
+    const int dp = DPL * 32;
+    constexpr int NC = DR_WARPS * DR_COLS;
+    // two buffers of DR_TOK tokens: q [dp], k [dp], a [dp], v [NC], beta, kq
+    const int tok_floats = 3 * dp + NC + 2;
+    const int seg = blockIdx.z, h = blockIdx.y, col_base = blockIdx.x * NC;
+    const int t_begin = cu_q[seg], t_end = cu_q[seg + 1];
+    if (t_end <= t_begin || positions[t_begin] < 0) return;      // an empty or a padding segment
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col0 = col_base + warp * DR_COLS;
+    const int hq = h / (H / G);
+    float* st = state + ((size_t)seg_slots[seg] * H + h) * (size_t)dv * d;
+    float S[DPL][DR_COLS];
+#pragma unroll
+    for (int r = 0; r < DPL; ++r)
+#pragma unroll
+        for (int c = 0; c < DR_COLS; ++c) {
+            const int i = lane + 32 * r, j = col0 + c;
+            S[r][c] = (i < d && j < dv) ? st[(size_t)j * d + i] : 0.f;
+        }
+    const int q_at = hq * d, k_at = G * d + hq * d, a_at = 2 * G * d + h * d, b_at = 2 * G * d + H * d + h,
+              kq_at = 2 * G * d + H * d + H + hq;
+    auto fetch = [&](int t0, int nt, float* buf) {
+        for (int idx = threadIdx.x; idx < nt * dp; idx += DR_WARPS * 32) {
+            const int tt = idx / dp, i = idx - tt * dp;
+            float* dst = buf + tt * tok_floats;
+            if (i < d) {
+                const float* src = prep + (size_t)(t0 + tt) * P;
+                dr_cp4(dst + i, src + q_at + i);
+                dr_cp4(dst + dp + i, src + k_at + i);
+                dr_cp4(dst + 2 * dp + i, src + a_at + i);
+            } else {
+                dst[i] = 0.f;
+                dst[dp + i] = 0.f;
+                dst[2 * dp + i] = 1.f;
+            }
+        }
+        for (int idx = threadIdx.x; idx < nt * (NC + 2); idx += DR_WARPS * 32) {
+            const int tt = idx / (NC + 2), c = idx - tt * (NC + 2);
+            float* dst = buf + tt * tok_floats + 3 * dp;
+            const float* src = prep + (size_t)(t0 + tt) * P;
+            if (c < NC) {
+                if (col_base + c < dv) dr_cp4(dst + c, v + (size_t)(t0 + tt) * v_stride + (size_t)h * dv + col_base + c);
+                else dst[c] = 0.f;
+            } else if (c == NC) dr_cp4(dst + c, src + b_at);
+            else dr_cp4(dst + c, src + kq_at);
+        }
+        dr_commit();
+    };
+    float* bufs[2] = {dsm, dsm + DR_TOK * tok_floats};
+    fetch(t_begin, min(DR_TOK, t_end - t_begin), bufs[0]);
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+    int round = 0;
+    for (int t0 = t_begin; t0 < t_end; t0 += DR_TOK, ++round) {
+        const int nt = min(DR_TOK, t_end - t0);
+        dr_wait_all();
+        __syncthreads();                    // this round's tokens are in; everyone is done with the other buffer
+        if (t0 + DR_TOK < t_end) fetch(t0 + DR_TOK, min(DR_TOK, t_end - t0 - DR_TOK), bufs[(round + 1) & 1]);
+        const float* buf = bufs[round & 1];
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* tk = buf + tt * tok_floats;
+            float vals[2 * DR_COLS];
+#pragma unroll
+            for (int c = 0; c < 2 * DR_COLS; ++c) vals[c] = 0.f;
+            float kr[DPL];
+#pragma unroll
+            for (int r = 0; r < DPL; ++r) {
+                const int i = lane + 32 * r;
+                const float qv = tk[i], kv = tk[dp + i], av = tk[2 * dp + i];
+                kr[r] = kv;
+#pragma unroll
+                for (int c = 0; c < DR_COLS; ++c) {
+                    const float s = S[r][c] * av;
+                    S[r][c] = s;
+                    vals[c] = fmaf(s, kv, vals[c]);
+                    vals[DR_COLS + c] = fmaf(s, qv, vals[DR_COLS + c]);
+                }
+            }
+            // eight sums over the 32 lanes by halving: after the three exchanges a lane holds one of them, after two more
+            // steps its total; sum number 4 * bit4 + 2 * bit3 + bit2 of the lane
+            float a4[4], a2[2], a1;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                a4[i] = (b4 ? vals[i + 4] : vals[i]) + __shfl_xor_sync(0xffffffffu, b4 ? vals[i] : vals[i + 4], 16);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                a2[i] = (b3 ? a4[i + 2] : a4[i]) + __shfl_xor_sync(0xffffffffu, b3 ? a4[i] : a4[i + 2], 8);
+            a1 = (b2 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, b2 ? a2[0] : a2[1], 4);
+            a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+            a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+            const float beta = tk[3 * dp + NC], kq = tk[3 * dp + NC + 1];
+            float u[DR_COLS];
+#pragma unroll
+            for (int c = 0; c < DR_COLS; ++c) {
+                const float r1 = __shfl_sync(0xffffffffu, a1, 8 * (c >> 1) + 4 * (c & 1));
+                u[c] = beta * (tk[3 * dp + warp * DR_COLS + c] - r1);
+            }
+#pragma unroll
+            for (int r = 0; r < DPL; ++r)
+#pragma unroll
+                for (int c = 0; c < DR_COLS; ++c) S[r][c] = fmaf(kr[r], u[c], S[r][c]);
+            // the lanes 16 + 8 (c >> 1) + 4 (c & 1) hold r2 of column c
+            if (b4 && (lane & 3) == 0) {
+                const int c = ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                const float uc = c == 0 ? u[0] : c == 1 ? u[1] : c == 2 ? u[2] : u[3];
+                if (col0 + c < dv) out[(size_t)(t0 + tt) * out_stride + (size_t)h * dv + col0 + c] = fmaf(uc, kq, a1);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < DPL; ++r)
+#pragma unroll
+        for (int c = 0; c < DR_COLS; ++c) {
+            const int i = lane + 32 * r, j = col0 + c;
+            if (i < d && j < dv) st[(size_t)j * d + i] = S[r][c];
+        }
+}
+
+PICO_API int pico_gated_delta_rule(const float* prep, const float* v, int v_stride, float* state, const int* seg_slots,
+                                   const int* cu_q, const int* positions, float* out, int out_stride, int S, int H, int G,
+                                   int d, int dv, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    if (H < 1 || G < 1 || H % G || d < 1 || d > 256 || dv < 1) return PICO_ERR_SIZE;
+    const int P = 2 * G * d + H * d + H + G;
+    const int dpl = (d + 31) / 32;
+    const dim3 grid((dv + DR_WARPS * DR_COLS - 1) / (DR_WARPS * DR_COLS), H, S);
+    if (grid.z > 65535 || grid.y > 65535) return PICO_ERR_SIZE;
+#define DR_LAUNCH(N)                                                                                                        \
+    do {                                                                                                                    \
+        const size_t smem = (size_t)2 * DR_TOK * (3 * N * 32 + DR_WARPS * DR_COLS + 2) * sizeof(float);                     \
+        if (smem > 48 * 1024)                                                                                               \
+            cudaFuncSetAttribute(gated_delta_rule_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+        pico_launch((gated_delta_rule_kernel<N>), grid, dim3(DR_WARPS * 32), smem, stream, prep, P, v, v_stride, state,     \
+                    seg_slots, cu_q, positions, out, out_stride, H, G, d, dv);                                              \
+    } while (0)
+    if (dpl <= 1) DR_LAUNCH(1);
+    else if (dpl <= 2) DR_LAUNCH(2);
+    else if (dpl <= 4) DR_LAUNCH(4);
+    else DR_LAUNCH(8);
+#undef DR_LAUNCH
+    return pico_launch_status();
+}

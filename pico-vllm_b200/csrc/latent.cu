@@ -1,6 +1,6 @@
 // Kernels of the latent-attention mixer: what stands between its matrix products.
 //
-// A token's down projection row holds, side by side, the query latent (q_rank), the key/value latent
+// A token's down projection row holds, side by side, the query latent (q_rank; 0: the queries are projected directly), the key/value latent
 // (kv_rank; absent in a layer that reads another layer's cache) and one gate logit per head.
 // latent_norm_store_kernel, one block of three warps per token (a warp per part):
 //   c_q  = u_q / sqrt(mean(u_q^2) + eps) * w_q                -> cq [T, q_rank]       (activation type)
@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(96) latent_norm_store_kernel(const TA* __restr
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const TA* row = proj + (size_t)t * proj_stride;
     if (warp == 0) {
-        rms_part<TA>(row + q_off, q_rank, wq, eps, cq + (size_t)t * q_rank, q_rank, lane);
+        if (q_rank > 0) rms_part<TA>(row + q_off, q_rank, wq, eps, cq + (size_t)t * q_rank, q_rank, lane);
     } else if (warp == 1) {
         const int slot = kv_rank > 0 && slots ? slots[t] : -1;
         if (slot >= 0) rms_part<TA>(row + kv_off, kv_rank, wkv, eps, cache + (size_t)slot * cache_row, cache_row, lane);
@@ -56,7 +56,7 @@ PICO_API int pico_latent_norm_store(const void* proj, int proj_stride, int q_off
                                     int cache_row, int g_off, int heads, float* gate, float eps, int T, int dtype,
                                     cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (q_rank <= 0 || heads <= 0 || kv_rank < 0 || (kv_rank > 0 && (cache_row < kv_rank || !cache || !wkv)))
+    if (q_rank < 0 || heads < 0 || kv_rank < 0 || (q_rank > 0 && (!wq || !cq)) || (heads > 0 && !gate) || (kv_rank > 0 && (cache_row < kv_rank || !cache || !wkv)))
         return PICO_ERR_SIZE;
     const int threads = 96;
     if (dtype == PICO_F32)

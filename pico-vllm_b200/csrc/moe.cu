@@ -24,7 +24,7 @@
 #define MOE_BN 64
 
 enum { MOE_GATE_UP = 0, MOE_DOWN = 1, MOE_UP_ACT = 2 };
-enum { MOE_ACT_SILU = 0, MOE_ACT_RELU2 = 1 };
+enum { MOE_ACT_SILU = 0, MOE_ACT_RELU2 = 1, MOE_ACT_CAPPED = 2 };   // CAPPED (gated experts): see moe_glu
 enum { MOE_SCORE_SOFTMAX_CHOSEN = 0, MOE_SCORE_SIGMOID = 1, MOE_SCORE_SOFTMAX_ALL = 2 };
 
 // TOK tokens per block (their rows of h in shared memory as float32, so that a warp reads an expert's router row once
@@ -33,7 +33,8 @@ template <typename TA, int TOK>
 __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h, const float* __restrict__ wr,
                                                         const float* __restrict__ br, int T, int D, int E, int top,
                                                         int mode, int* __restrict__ idx, float* __restrict__ wgt,
-                                                        const float* __restrict__ choice_bias, float weight_scale) {
+                                                        const float* __restrict__ choice_bias, float weight_scale,
+                                                        int groups, int groups_keep, int renorm) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float rsm[];       // TOK rows of D floats (D rounded up to 4), then TOK x E logits (twice for mode 2)
@@ -96,6 +97,29 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h
             zt[e] = p + (choice_bias ? choice_bias[e] : 0.f);
         }
         __syncwarp();
+        // groups of neighbouring experts: only the groups_keep groups whose best number (score + bias) is largest stay in
+        // the choice (the lower group first among equals); the others count as minus infinity
+        if (groups > 1 && groups_keep < groups) {
+            float* gbest = z + 2 * TOK * E + warp * E;          // [groups], then which groups stay
+            const int per = E / groups;
+            for (int g = lane; g < groups; g += 32) {
+                float b = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, zt[e]);
+                gbest[g] = b;
+            }
+            __syncwarp();
+            for (int g = lane; g < groups; g += 32) {
+                const float mine_b = gbest[g];
+                int ahead = 0;                                   // groups that come before this one in the order
+                for (int o = 0; o < groups; ++o) {
+                    const float ob = gbest[o];
+                    ahead += (ob > mine_b || (ob == mine_b && o < g)) ? 1 : 0;
+                }
+                if (ahead >= groups_keep)
+                    for (int e = g * per; e < (g + 1) * per; ++e) zt[e] = -INFINITY;
+            }
+            __syncwarp();
+        }
     }
     float first = 0.f, sum = 0.f, mine = 0.f;    // lane j keeps the j-th chosen logit (top <= 32)
     int mine_e = 0;
@@ -124,7 +148,9 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h
     }
     if (lane < top) {
         idx[(size_t)t * top + lane] = mine_e;
-        wgt[(size_t)t * top + lane] = mode == MOE_SCORE_SOFTMAX_CHOSEN ? mine / sum : mine;
+        // renorm (softmax over all): the chosen scores divided by their sum; sum holds them times weight_scale
+        wgt[(size_t)t * top + lane] = mode == MOE_SCORE_SOFTMAX_CHOSEN ? mine / sum
+                                      : renorm ? mine / (sum / weight_scale + 1e-20f) : mine;
     }
 }
 
@@ -172,6 +198,16 @@ __device__ __forceinline__ int moe_find_expert(const int* __restrict__ tile_star
 }
 
 __device__ __forceinline__ float moe_silu(float g) { return g / (1.0f + expf(-g)); }
+// What a gated expert makes of its gate and up products: silu(g) u, or with a cap L (MOE_ACT_CAPPED)
+// g' sigmoid(1.702 g') (u' + 1) with g' = min(g, L) and u' = clamp(u, -L, L).
+__device__ __forceinline__ float moe_glu(float g, float u, int act, float limit) {
+    if (act == MOE_ACT_CAPPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return moe_silu(g) * u;
+}
 __device__ __forceinline__ float moe_act(float u, int act) {
     if (act == MOE_ACT_RELU2) { const float r = fmaxf(u, 0.f); return r * r; }
     return moe_silu(u);
@@ -189,7 +225,7 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
                                                            const int* __restrict__ tile_start,
                                                            const int* __restrict__ perm, int E, int top, int N, int K,
                                                            bf16* __restrict__ act, float* __restrict__ out2,
-                                                           const float* __restrict__ wgt, int act_kind) {
+                                                           const float* __restrict__ wgt, int act_kind, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int NB = EPI == MOE_GATE_UP ? 2 : 1;
@@ -281,7 +317,7 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
                 if (n >= N) continue;
                 if (EPI == MOE_GATE_UP) {
                     const float g = acc[0][j][half * 2 + c], u = acc[NB - 1][j][half * 2 + c];
-                    act[(size_t)p * N + n] = __float2bfloat16_rn(moe_silu(g) * u);
+                    act[(size_t)p * N + n] = __float2bfloat16_rn(moe_glu(g, u, act_kind, limit));
                 } else if (EPI == MOE_UP_ACT) {
                     act[(size_t)p * N + n] = __float2bfloat16_rn(moe_act(wrow * acc[0][j][half * 2 + c], act_kind));
                 } else {
@@ -299,7 +335,7 @@ __global__ void __launch_bounds__(256) moe_gemm_simple_kernel(const TA* __restri
                                                               const int* __restrict__ tile_start,
                                                               const int* __restrict__ perm, int E, int top, int N, int K,
                                                               TA* __restrict__ act, float* __restrict__ out2,
-                                                              const float* __restrict__ wgt, int act_kind) {
+                                                              const float* __restrict__ wgt, int act_kind, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int NB = EPI == MOE_GATE_UP ? 2 : 1;
@@ -367,7 +403,7 @@ __global__ void __launch_bounds__(256) moe_gemm_simple_kernel(const TA* __restri
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             if (EPI == MOE_GATE_UP)
-                act[(size_t)p * N + n] = from_f32<TA>(moe_silu(acc[0][i][j]) * acc[NB - 1][i][j]);
+                act[(size_t)p * N + n] = from_f32<TA>(moe_glu(acc[0][i][j], acc[NB - 1][i][j], act_kind, limit));
             else if (EPI == MOE_UP_ACT)
                 act[(size_t)p * N + n] = from_f32<TA>(moe_act(wrow * acc[0][i][j], act_kind));
             else
@@ -397,19 +433,23 @@ __global__ void moe_combine_kernel(const float* __restrict__ out2, const float* 
 
 // h [T, D]; wr float32 [E, D]; br float32 [E] or nullptr; idx int32 [T, top]; wgt float32 [T, top].
 PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int T, int D, int E, int top, int mode,
-                            int* idx, float* wgt, int dtype, const float* choice_bias, float weight_scale, cudaStream_t stream) {
+                            int* idx, float* wgt, int dtype, const float* choice_bias, float weight_scale, int groups,
+                            int groups_keep, int renorm, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E < 1 || top < 1 || top > E || top > 32 || E > 8192 || mode < 0 || mode > 2) return PICO_ERR_SIZE;
+    if (groups < 1 || E % groups || groups_keep < 1 || groups_keep > groups) return PICO_ERR_SIZE;
+    if ((groups > 1 || renorm) && mode != MOE_SCORE_SOFTMAX_ALL) return PICO_ERR_SIZE;
+    if (renorm && !(weight_scale != 0.f)) return PICO_ERR_SIZE;
     // four tokens a block when there are many (the router matrix is read once per block), one otherwise
     const int tok = T >= 512 ? 4 : 1;
-    const size_t smem = ((size_t)tok * ((D + 3) & ~3) + (size_t)2 * tok * E) * sizeof(float);
+    const size_t smem = ((size_t)tok * ((D + 3) & ~3) + (size_t)3 * tok * E) * sizeof(float);
     if (smem > 200 * 1024) return PICO_ERR_SIZE;
     const dim3 grid((T + tok - 1) / tok);
 #define LAUNCH_ROUTE(TA, TOK)                                                                                             \
     do {                                                                                                                  \
         if (smem > 48 * 1024)                                                                                             \
             cudaFuncSetAttribute(moe_route_kernel<TA, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-        pico_launch((moe_route_kernel<TA, TOK>), grid, dim3(256), smem, stream, (const TA*)h, wr, br, T, D, E, top, mode, idx, wgt, choice_bias, weight_scale); \
+        pico_launch((moe_route_kernel<TA, TOK>), grid, dim3(256), smem, stream, (const TA*)h, wr, br, T, D, E, top, mode, idx, wgt, choice_bias, weight_scale, groups, groups_keep, renorm); \
     } while (0)
     if (dtype == PICO_F32) {
         if (tok == 4) LAUNCH_ROUTE(float, 4); else LAUNCH_ROUTE(float, 1);
@@ -535,15 +575,15 @@ PICO_API int pico_moe_combine_placed(const void* ys, const int* place, const flo
 // bm: the rows per tile that pico_moe_group was given (16 only for bfloat16 with K a multiple of 8).
 PICO_API int pico_moe_gemm(const void* a, const void* w, const int* offsets, const int* tile_start, const int* perm,
                            int n, int E, int top, int N, int K, int epi, int bm, void* act, float* out2,
-                           const float* wgt, int act_kind, int dtype, cudaStream_t stream) {
+                           const float* wgt, int act_kind, float limit, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (N < 1 || K < 1 || epi < 0 || epi > 2 || act_kind < 0 || act_kind > 1 || (bm != 16 && bm != MOE_BM)) return PICO_ERR_SIZE;
+    if (N < 1 || K < 1 || epi < 0 || epi > 2 || act_kind < 0 || act_kind > 2 || (act_kind == MOE_ACT_CAPPED && epi != MOE_GATE_UP) || (bm != 16 && bm != MOE_BM)) return PICO_ERR_SIZE;
     if (bm == 16 && !(dtype == PICO_BF16 && K % 8 == 0)) return PICO_ERR_SIZE;
     const dim3 grid(moe_max_tiles(n, E, bm), (N + MOE_BN - 1) / MOE_BN);
     if (grid.y > 65535) return PICO_ERR_SIZE;
 #define MOE_MMA(EPI_, BM_, BK_)                                                                                             \
     pico_launch((moe_gemm_mma_kernel<EPI_, BM_, BK_>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets, \
-                tile_start, perm, E, top, N, K, (bf16*)act, out2, wgt, act_kind)
+                tile_start, perm, E, top, N, K, (bf16*)act, out2, wgt, act_kind, limit)
     if (dtype == PICO_BF16 && K % 8 == 0) {
         if (epi == MOE_GATE_UP) {
             if (bm == 16) MOE_MMA(MOE_GATE_UP, 16, 32); else MOE_MMA(MOE_GATE_UP, 64, 32);
@@ -555,7 +595,7 @@ PICO_API int pico_moe_gemm(const void* a, const void* w, const int* offsets, con
     } else if (dtype == PICO_BF16) {
 #define MOE_SIMPLE(TA_, EPI_)                                                                                              \
     pico_launch((moe_gemm_simple_kernel<TA_, EPI_>), grid, dim3(256), 0, stream, (const TA_*)a, (const TA_*)w, offsets,     \
-                tile_start, perm, E, top, N, K, (TA_*)act, out2, wgt, act_kind)
+                tile_start, perm, E, top, N, K, (TA_*)act, out2, wgt, act_kind, limit)
         if (epi == MOE_GATE_UP) MOE_SIMPLE(bf16, MOE_GATE_UP);
         else if (epi == MOE_UP_ACT) MOE_SIMPLE(bf16, MOE_UP_ACT);
         else MOE_SIMPLE(bf16, MOE_DOWN);

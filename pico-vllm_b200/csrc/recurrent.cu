@@ -493,7 +493,7 @@ __global__ void __launch_bounds__(256)
 causal_conv_silu_kernel(const TA* __restrict__ proj, int row_stride, int c_off, const float* __restrict__ w,
                         const float* __restrict__ b, const float* __restrict__ conv_state, const int* __restrict__ tok_seg,
                         const int* __restrict__ seg_slots, const int* __restrict__ cu_q, const int* __restrict__ positions,
-                        int C, int taps, int T, int tpb, float* __restrict__ out) {
+                        int C, int taps, int T, int tpb, float* __restrict__ out, int act) {
     pdl_launch_dependents();
     pdl_wait();
     // a block takes tpb consecutive tokens (one when the step is short) of 256 channels, a thread one channel: it walks the
@@ -532,7 +532,7 @@ causal_conv_silu_kernel(const TA* __restrict__ proj, int row_stride, int c_off, 
             float acc = bias;
 #pragma unroll
             for (int k = 0; k < M; ++k) acc = fmaf(wt[k], win[k], acc);      // oldest first; unused taps weigh zero
-            out[(size_t)t * C + c] = rc_silu(acc);
+            out[(size_t)t * C + c] = act ? rc_silu(acc) : acc;
 #pragma unroll
             for (int k = 0; k < M - 1; ++k) win[k] = win[k + 1];
         }
@@ -562,7 +562,7 @@ __global__ void conv_state_kernel(const TA* __restrict__ proj, int row_stride, i
 // conv_state float32 [slots, taps - 1, C]; out float32 [T, C].
 PICO_API int pico_causal_conv_silu(const void* proj, int row_stride, int c_off, const float* w, const float* b,
                                    float* conv_state, const int* tok_seg, const int* seg_slots, const int* cu_q,
-                                   const int* positions, float* out, int T, int S, int C, int taps, int dtype,
+                                   const int* positions, float* out, int T, int S, int C, int taps, int dtype, int act,
                                    cudaStream_t stream) {
     if (T <= 0 || S <= 0) return 0;
     if (C < 1 || taps < 1 || taps > CONV_MAX_TAPS || S > 65535 || (C + 255) / 256 > 65535) return PICO_ERR_SIZE;
@@ -572,10 +572,10 @@ PICO_API int pico_causal_conv_silu(const void* proj, int row_stride, int c_off, 
     do {                                                                                                                 \
         if (taps <= 4)                                                                                                   \
             pico_launch((causal_conv_silu_kernel<TA, 4>), dim3(blocks, (C + 255) / 256), dim3(256), 0, stream, (const TA*)proj,  \
-                        row_stride, c_off, w, b, (const float*)conv_state, tok_seg, seg_slots, cu_q, positions, C, taps, T, tpb, out); \
+                        row_stride, c_off, w, b, (const float*)conv_state, tok_seg, seg_slots, cu_q, positions, C, taps, T, tpb, out, act); \
         else                                                                                                             \
             pico_launch((causal_conv_silu_kernel<TA, CONV_MAX_TAPS>), dim3(blocks, (C + 255) / 256), dim3(256), 0, stream, (const TA*)proj, \
-                        row_stride, c_off, w, b, (const float*)conv_state, tok_seg, seg_slots, cu_q, positions, C, taps, T, tpb, out); \
+                        row_stride, c_off, w, b, (const float*)conv_state, tok_seg, seg_slots, cu_q, positions, C, taps, T, tpb, out, act); \
         if (taps > 1)                                                                                                    \
             pico_launch((conv_state_kernel<TA>), dim3((C + 127) / 128, S), dim3(128), 0, stream, (const TA*)proj, row_stride, \
                         c_off, conv_state, seg_slots, cu_q, positions, C, taps);                                         \

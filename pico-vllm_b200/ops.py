@@ -80,12 +80,12 @@ def library():
         "pico_scale_softcap": [vp, i32, i32, i32, f32, f32, vp],
         "pico_latent_norm_store": [vp, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, vp, f32, i32, i32, vp],
         "pico_head_scale": [vp, vp, i32, i32, i32, i32, vp],
-        "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, f32, vp],
+        "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, f32, i32, i32, i32, vp],
         "pico_moe_group": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
         "pico_moe_tile_rows": [i32, i32, i32, i32, i32],
         "pico_moe_gather": [vp, vp, i32, i32, i32, vp, vp],
         "pico_moe_combine_placed": [vp, vp, vp, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp],
-        "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, i32, i32, vp],
+        "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, i32, f32, i32, vp],
         "pico_moe_combine": [vp, vp, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp],
         "pico_moe_scaled_act": [vp, vp, vp, i32, i32, i32, vp, i32, vp],
         "pico_qk_norm_rope_store": [vp, i32, vp, vp, vp, f32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
@@ -103,9 +103,17 @@ def library():
         "pico_mlstm_prepare": [vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32,
                                i32, i32, i32, i32, vp],
         "pico_hgrn2_prepare": [vp, i32, i32, i32, i32, vp, vp, vp, i32, i32, i32, i32, vp],
-        "pico_causal_conv_silu": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+        "pico_causal_conv_silu": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
         "pico_mamba2_prepare": [vp, i32, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp],
         "pico_group_rms_norm": [vp, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, vp],
+        "pico_delta_prepare": [vp, i32, i32, i32, vp, i32, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, f32, f32, i32, vp],
+        "pico_gated_delta_rule": [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+        "pico_pair_rope_norm_store": [vp, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp, f32, vp, vp, vp, vp, i32, i32, i32, i32,
+                                      i32, i32, i32, i32, vp],
+        "pico_sum_add_norm": [vp, vp, vp, i32, f32, f32, vp, vp, i32, f32, f32, vp, vp, i32, f32, f32, vp, i32, f32, vp, vp, i32,
+                              i32, i32, vp],
+        "pico_gelu_gate_rows": [vp, vp, i32, i32, vp, vp, i32, i32, i32, vp, i32, vp],
+        "pico_capped_glu": [vp, i32, i32, i32, f32, f32, i32, vp, i32, vp],
         "pico_whole_norm_store": [vp, i32, i32, i32, i32, vp, vp, f32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                   i32, vp],
     }
@@ -809,18 +817,19 @@ def scale_softcap(logits: torch.Tensor, scale: float, cap: Optional[float]) -> t
 
 # ------------------------------------------------------------------------------------------
 # Latent attention: what stands between its matrix products.
-def latent_norm_store(proj: torch.Tensor, q_off: int, q_rank: int, q_weight: torch.Tensor, kv_off: int, kv_rank: int,
+def latent_norm_store(proj: torch.Tensor, q_off: int, q_rank: int, q_weight: Optional[torch.Tensor], kv_off: int, kv_rank: int,
                       kv_weight: Optional[torch.Tensor], slots: Optional[torch.Tensor], cache: Optional[torch.Tensor],
                       g_off: int, heads: int, eps: float):
     """From a token's down projection row ``proj[t]`` (query latent at q_off, key/value latent at kv_off, one gate
     logit per head at g_off): the RMS-normed query latent [T, q_rank], the RMS-normed key/value latent into cache
     row ``slots[t]`` (``cache`` [..., row width >= kv_rank], zero beyond kv_rank; nothing for a slot of -1;
-    kv_rank 0: no key/value part), and sigmoid of the gate logits (float32 [T, heads]).  Returns (cq, gate)."""
+    kv_rank 0: no key/value part), and sigmoid of the gate logits (float32 [T, heads]).  ``q_rank`` 0: no query latent,
+    ``heads`` 0: no gate; the part that is absent comes back as None.  Returns (cq, gate)."""
     _cuda(proj, q_weight, kv_weight, slots, cache)
     T = proj.shape[0]
     if proj.stride(1) != 1 or max(q_off + q_rank, kv_off + kv_rank, g_off + heads) > proj.shape[1]:
         raise KernelError("latent_norm_store: the projection row is narrower than its parts")
-    if q_weight.dtype != torch.float32 or q_weight.shape != (q_rank,):
+    if q_rank > 0 and (q_weight is None or q_weight.dtype != torch.float32 or q_weight.shape != (q_rank,)):
         raise KernelError("latent_norm_store: q_weight must be float32 [q_rank]")
     row = 0
     if kv_rank > 0:
@@ -830,8 +839,8 @@ def latent_norm_store(proj: torch.Tensor, q_off: int, q_rank: int, q_weight: tor
                 or cache.dtype != proj.dtype or not cache.is_contiguous() or cache.shape[-1] < kv_rank:
             raise KernelError("latent_norm_store: needs int32 slots and a contiguous cache of the activation type")
         row = cache.shape[-1]
-    cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device)
-    gate = torch.empty((T, heads), dtype=torch.float32, device=proj.device)
+    cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device) if q_rank > 0 else None
+    gate = torch.empty((T, heads), dtype=torch.float32, device=proj.device) if heads > 0 else None
     _check(library().pico_latent_norm_store(_ptr(proj), proj.stride(0), q_off, q_rank, _ptr(q_weight), _ptr(cq), kv_off,
                                             kv_rank, _ptr(kv_weight), _ptr(slots), _ptr(cache) if kv_rank > 0 else None,
                                             row, g_off, heads, _ptr(gate), float(eps), T, _dtype_code(proj), _stream()),
@@ -877,15 +886,19 @@ def head_scale(o: torch.Tensor, gate: torch.Tensor, heads: int) -> torch.Tensor:
 # ------------------------------------------------------------------------------------------
 # Routed experts.
 MOE_SCORE_SOFTMAX_CHOSEN, MOE_SCORE_SIGMOID, MOE_SCORE_SOFTMAX_ALL = 0, 1, 2
-MOE_ACT_SILU, MOE_ACT_RELU2 = 0, 1
+MOE_ACT_SILU, MOE_ACT_RELU2, MOE_ACT_CAPPED = 0, 1, 2
 
 
 def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optional[torch.Tensor], top: int,
-              scoring: int = MOE_SCORE_SOFTMAX_CHOSEN, choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0):
+              scoring: int = MOE_SCORE_SOFTMAX_CHOSEN, choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0,
+              groups: int = 1, groups_keep: int = 1, renorm: bool = False):
     """Router logits z = h W^T + b in float32, the ``top`` largest per token and the softmax over those alone
     (``scoring`` MOE_SCORE_SIGMOID: each chosen expert's weight is sigmoid(z) of its own logit, not renormalised;
     MOE_SCORE_SOFTMAX_ALL: an expert's score is its share of the softmax over all E logits, the ``top`` largest of score +
-    ``choice_bias`` (float32 [E]) are chosen, and the weight is the score itself times ``weight_scale``, not renormalised).
+    ``choice_bias`` (float32 [E]) are chosen, and the weight is the score itself times ``weight_scale``, not renormalised -
+    or, with ``renorm``, the score divided by the sum of the chosen scores (+ 1e-20) times ``weight_scale``; with ``groups`` > 1
+    the experts form that many equal runs of neighbours and only the experts of the ``groups_keep`` runs whose largest
+    score + choice_bias is largest can be chosen).
     h [T, D]; router_weight float32 [E, D]; router_bias float32 [E] or None.  Returns (idx int32 [T, top],
     weights float32 [T, top])."""
     _cuda(h, router_weight, router_bias)
@@ -898,10 +911,15 @@ def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optiona
         raise KernelError("moe_route: the router bias must be float32 [E]")
     if choice_bias is not None and (choice_bias.dtype != torch.float32 or choice_bias.shape != (E,) or not choice_bias.is_cuda):
         raise KernelError("moe_route: the choice bias must be float32 [E]")
+    if groups < 1 or E % groups or not 1 <= groups_keep <= groups or top > E // groups * groups_keep:
+        raise KernelError(f"moe_route: {E} experts in {groups} groups of which {groups_keep} stay cannot give {top} choices")
+    if (groups > 1 or renorm) and scoring != MOE_SCORE_SOFTMAX_ALL:
+        raise KernelError("moe_route: groups and renormalised weights are built for the softmax over all experts")
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     wgt = torch.empty((T, top), dtype=torch.float32, device=h.device)
     _check(library().pico_moe_route(_ptr(h), _ptr(router_weight), _ptr(router_bias), T, D, E, top, int(scoring), _ptr(idx), _ptr(wgt),
-                                    _dtype_code(h), _ptr(choice_bias), float(weight_scale), _stream()),
+                                    _dtype_code(h), _ptr(choice_bias), float(weight_scale), int(groups), int(groups_keep),
+                                    1 if renorm else 0, _stream()),
            f"moe_route ({E} experts, top {top})")
     _count()
     return idx, wgt
@@ -909,7 +927,7 @@ def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optiona
 
 def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_weight: torch.Tensor,
                 down_weight: torch.Tensor, gated: bool = True, act: int = MOE_ACT_SILU, weight_on_input: bool = False,
-                base: Optional[torch.Tensor] = None, identity: int = 0) -> torch.Tensor:
+                base: Optional[torch.Tensor] = None, identity: int = 0, limit: float = 0.0) -> torch.Tensor:
     """The routed experts' sum.  With e = idx[t, j]:
 
     gated, weight on the output (the default):  sum_j wgt[t, j] * down[e] (silu(gate[e] h_t) * (up[e] h_t)),
@@ -921,7 +939,9 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
     The (token, j) entries are listed per expert on the device, the two products run as grouped products over those
     lists, and the sum is taken in float32; ``base`` [T, D] (a shared expert's output) is added in the same kernel.
     down_weight [E, D, ff]; all in h's type.  ``identity`` n: idx may also name E .. E + n - 1, experts without tensors whose
-    output is their input (wgt[t, j] * h_t; weight on the output only).  Returns [T, D] in h's type."""
+    output is their input (wgt[t, j] * h_t; weight on the output only).  ``act`` MOE_ACT_CAPPED (gated experts): with
+    g' = min(gate h, limit) and u' = clamp(up h, -limit, limit) the expert is down (g' sigmoid(1.702 g') (u' + 1)).
+    Returns [T, D] in h's type."""
     _cuda(h, idx, wgt, gate_up_weight, down_weight, base)
     T, D = h.shape
     top = idx.shape[1]
@@ -935,8 +955,10 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
     if idx.dtype != torch.int32 or wgt.dtype != torch.float32 or idx.shape != (T, top) or wgt.shape != (T, top) \
             or not (idx.is_contiguous() and wgt.is_contiguous()):
         raise KernelError("moe_experts: idx int32 [T, top] and wgt float32 [T, top]")
-    if gated and (act != MOE_ACT_SILU or weight_on_input):
-        raise KernelError("moe_experts: gated experts are built with silu and the weight on the output only")
+    if gated and (act not in (MOE_ACT_SILU, MOE_ACT_CAPPED) or weight_on_input):
+        raise KernelError("moe_experts: gated experts are built with silu or the capped form and the weight on the output only")
+    if act == MOE_ACT_CAPPED and not (gated and limit > 0.0):
+        raise KernelError("moe_experts: the capped form is for gated experts and needs a positive limit")
     if base is not None and (base.shape != (T, D) or base.dtype != h.dtype or not base.is_contiguous()):
         raise KernelError("moe_experts: base must be contiguous [T, D] in h's type")
     if identity and (weight_on_input or identity < 0):
@@ -966,8 +988,11 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
             ends = offsets[1:E + 1]
             gu = torch._grouped_mm(xs, gate_up_weight.transpose(1, 2), offs=ends)
             if gated:
-                a = torch.empty((n, ff), dtype=h.dtype, device=h.device)
-                swiglu(gu, a)
+                if act == MOE_ACT_CAPPED:
+                    a = capped_glu(gu, ff, limit)
+                else:
+                    a = torch.empty((n, ff), dtype=h.dtype, device=h.device)
+                    swiglu(gu, a)
             else:
                 a = gu
                 _check(lib.pico_moe_scaled_act(_ptr(gu), _ptr(perm), _ptr(in_w), n, ff, int(act), _ptr(a), code, st),
@@ -982,10 +1007,10 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
                 raise
     a = torch.empty((n, ff), dtype=h.dtype, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(h), _ptr(gate_up_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, ff, D,
-                             0 if gated else 2, bm, _ptr(a), None, _ptr(in_w), int(act), code, st), "moe_gemm (up)")
+                             0 if gated else 2, bm, _ptr(a), None, _ptr(in_w), int(act), float(limit), code, st), "moe_gemm (up)")
     out2 = torch.empty((n, D), dtype=torch.float32, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(a), _ptr(down_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, D, ff,
-                             1, bm, None, _ptr(out2), None, 0, code, st), "moe_gemm (down)")
+                             1, bm, None, _ptr(out2), None, 0, 0.0, code, st), "moe_gemm (down)")
     _check(lib.pico_moe_combine(_ptr(out2), _ptr(out_w), T, top, D, _ptr(y), _ptr(base), code, _ptr(eidx), E, _ptr(hsrc), st),
            "moe_combine")
     _count(4)
@@ -1298,11 +1323,11 @@ def hgrn2_prepare(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias
 
 def causal_conv_silu(proj: torch.Tensor, c_off: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
                      conv_state: torch.Tensor, tok_seg: torch.Tensor, seg_slots: torch.Tensor, cu_q: torch.Tensor,
-                     positions: torch.Tensor) -> torch.Tensor:
+                     positions: torch.Tensor, act: bool = True) -> torch.Tensor:
     """silu of a causal convolution per channel over the tokens of each segment: out[t, c] = silu(b[c] + sum_j w[c, j] *
     in(t - (taps - 1) + j, c)), the last tap on the token itself.  The channels are columns c_off .. of ``proj``; inputs from
     before the segment come from ``conv_state`` float32 [slots, taps - 1, C] (zero at a request's start), which afterwards
-    holds the segment's last taps - 1 inputs.  Returns float32 [T, C]."""
+    holds the segment's last taps - 1 inputs.  ``act`` False: the convolution alone, no silu.  Returns float32 [T, C]."""
     _cuda(proj, weight, bias, conv_state, tok_seg, seg_slots, cu_q, positions)
     T, S = proj.shape[0], seg_slots.shape[0]
     C, taps = weight.shape
@@ -1315,7 +1340,7 @@ def causal_conv_silu(proj: torch.Tensor, c_off: int, weight: torch.Tensor, bias:
     out = torch.empty((T, C), dtype=torch.float32, device=proj.device)
     _check(library().pico_causal_conv_silu(_ptr(proj), proj.stride(0), c_off, _ptr(weight), _ptr(bias), _ptr(conv_state),
                                            _ptr(tok_seg), _ptr(seg_slots), _ptr(cu_q), _ptr(positions), _ptr(out), T, S, C, taps,
-                                           _dtype_code(proj), _stream()), f"causal_conv_silu ({taps} taps)")
+                                           _dtype_code(proj), 1 if act else 0, _stream()), f"causal_conv_silu ({taps} taps)")
     _count(2 if taps > 1 else 1)
     return out
 
@@ -1403,3 +1428,164 @@ def whole_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w
                                            kv_heads, dim, vdim, row, page_size, _dtype_code(proj), _stream()), "whole_norm_store")
     _count()
     return q_out
+
+
+# ------------------------------------------------------------------------------------------ the delta rule; neighbours that turn together
+def delta_prepare(xc: torch.Tensor, q_off: int, k_off: int, proj: torch.Tensor, b_off: int, dt: torch.Tensor,
+                  dt_bias: Optional[torch.Tensor], a_log: torch.Tensor, heads: int, kv_heads: int, dim: int,
+                  unit_eps: float = 1e-6) -> torch.Tensor:
+    """The float32 inputs of the gated delta rule.  ``xc`` float32 rows hold ``kv_heads`` query heads at q_off and as many key
+    heads at k_off (``dim`` each); ``proj`` (activation type) one logit per head at b_off; ``dt`` [T, heads * dim] (activation
+    type) the decay's argument, ``dt_bias`` float32 [heads * dim], ``a_log`` float32 [heads].  Returns float32 [T, P],
+    P = 2 G d + H d + H + G:  q / sqrt(|q|^2 + unit_eps) * d^-1/2  |  k / sqrt(|k|^2 + unit_eps)  |
+    exp(-exp(a_log) softplus(dt + dt_bias))  |  sigmoid(logit)  |  k . q."""
+    _cuda(xc, proj, dt, dt_bias, a_log)
+    T = xc.shape[0]
+    _f32_rows(xc, "delta_prepare: xc")
+    H, G, d = heads, kv_heads, dim
+    if H % G or max(q_off, k_off) + G * d > xc.shape[1] or proj.dim() != 2 or proj.stride(1) != 1 or b_off + H > proj.shape[1] \
+            or dt.dim() != 2 or dt.stride(1) != 1 or dt.shape != (T, H * d) or dt.dtype != proj.dtype or proj.shape[0] != T:
+        raise KernelError("delta_prepare: a row is narrower than its heads")
+    if a_log.dtype != torch.float32 or a_log.shape != (H,) or (dt_bias is not None and (dt_bias.dtype != torch.float32 or dt_bias.shape != (H * d,))):
+        raise KernelError("delta_prepare: a_log float32 [heads], dt_bias float32 [heads * dim]")
+    prep = torch.empty((T, 2 * G * d + H * d + H + G), dtype=torch.float32, device=xc.device)
+    _check(library().pico_delta_prepare(_ptr(xc), xc.stride(0), q_off, k_off, _ptr(proj), proj.stride(0), b_off, _ptr(dt),
+                                        dt.stride(0), _ptr(dt_bias), _ptr(a_log), _ptr(prep), T, H, G, d, float(d) ** -0.5,
+                                        float(unit_eps), _dtype_code(proj), _stream()), "delta_prepare")
+    _count()
+    return prep
+
+
+def gated_delta_rule(prep: torch.Tensor, v: torch.Tensor, state: torch.Tensor, seg_slots: torch.Tensor, cu_q: torch.Tensor,
+                     positions: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Per head h, token by token in the order of each segment, from and into ``state`` float32 [slots, heads, vdim, dim] (S
+    transposed; row ``seg_slots[s]``):  S <- diag(a) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  ``prep``: the rows
+    :func:`delta_prepare` made (head h reads query and key head h // (heads / kv_heads)); ``v`` float32 rows with head h's values
+    at h * vdim (a column slice is fine).  A segment whose first position is negative is padding.  Returns o float32
+    [T, heads * vdim]."""
+    _cuda(prep, v, state, seg_slots, cu_q, positions)
+    _f32_rows(v, "gated_delta_rule: v")
+    T, S = prep.shape[0], seg_slots.shape[0]
+    H, G, d = heads, kv_heads, dim
+    if prep.dtype != torch.float32 or not prep.is_contiguous() or prep.shape[1] != 2 * G * d + H * d + H + G or v.shape[0] != T \
+            or v.shape[1] < H * vdim:
+        raise KernelError("gated_delta_rule: prep must be what delta_prepare returns and v hold every head's values")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (H, vdim, d):
+        raise KernelError("gated_delta_rule: state must be contiguous float32 [slots, heads, vdim, dim]")
+    if d > 256:
+        raise KernelError(f"gated_delta_rule: key size {d} above 256 is not built")
+    for t in (seg_slots, cu_q, positions):
+        if t.dtype != torch.int32:
+            raise KernelError("gated_delta_rule: index tensors must be int32")
+    if cu_q.shape[0] != S + 1 or positions.shape[0] != T:
+        raise KernelError("gated_delta_rule: cu_q must have one more entry than seg_slots, positions one per token")
+    out = torch.empty((T, H * vdim), dtype=torch.float32, device=prep.device)
+    _check(library().pico_gated_delta_rule(_ptr(prep), _ptr(v), v.stride(0), _ptr(state), _ptr(seg_slots), _ptr(cu_q),
+                                           _ptr(positions), _ptr(out), out.stride(0), S, H, G, d, vdim, _stream()),
+           f"gated_delta_rule (dim {d})")
+    _count()
+    return out
+
+
+def pair_rope_norm_store(x: torch.Tensor, q_off: int, k_off: int, v_off: int, positions: torch.Tensor,
+                         inv_freq: Optional[torch.Tensor], norm: bool, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                         eps: float, slots: Optional[torch.Tensor], k_pages: torch.Tensor, v_pages: torch.Tensor, heads: int,
+                         kv_heads: int, dim: int, vdim: int, row: int, page_size: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """From float32 rows ``x`` (queries at q_off, keys at k_off, values at v_off): every query and key head turned in its
+    first 2 * len(inv_freq) dimensions, dimension 2i with 2i + 1 by position * inv_freq[i], then (``norm``) divided by its root
+    mean square over ``dim`` (eps inside the root) and multiplied by ``q_w`` / ``k_w`` (float32 [dim]; None: no weight); keys
+    and untouched values written to the token's place in the pages [pages, kv_heads, page_size, row] (``slots`` int32; -1 or
+    None: not stored), heads padded with zeros to ``row``.  Returns the queries [T, heads * row] in ``out_dtype``."""
+    _cuda(x, positions, inv_freq, q_w, k_w, slots, k_pages, v_pages)
+    _f32_rows(x, "pair_rope_norm_store: x")
+    T = x.shape[0]
+    if max(q_off + heads * dim, k_off + kv_heads * dim, v_off + kv_heads * vdim) > x.shape[1]:
+        raise KernelError("pair_rope_norm_store: a row is narrower than its heads")
+    rot = 0 if inv_freq is None else 2 * inv_freq.shape[0]
+    if positions.dtype != torch.int32 or (inv_freq is not None and inv_freq.dtype != torch.float32) or rot > dim:
+        raise KernelError("pair_rope_norm_store: positions int32, inv_freq float32 [<= dim / 2]")
+    for w in (q_w, k_w):
+        if w is not None and (w.dtype != torch.float32 or w.shape != (dim,)):
+            raise KernelError("pair_rope_norm_store: norm weights must be float32 [dim]")
+    for t in (k_pages, v_pages):
+        if t.dtype != out_dtype or t.dim() != 4 or tuple(t.shape[1:]) != (kv_heads, page_size, row) or not t.is_contiguous():
+            raise KernelError("pair_rope_norm_store: pages must be contiguous [pages, kv_heads, page_size, row] in the activation type")
+    if slots is not None and (slots.dtype != torch.int32 or slots.shape[0] != T):
+        raise KernelError("pair_rope_norm_store: slots must be int32 [T]")
+    q_out = torch.empty((T, heads * row), dtype=out_dtype, device=x.device)
+    _check(library().pico_pair_rope_norm_store(_ptr(x), x.stride(0), q_off, k_off, v_off, _ptr(positions), _ptr(inv_freq), rot,
+                                               1 if norm else 0, _ptr(q_w), _ptr(k_w), float(eps), _ptr(slots), _ptr(k_pages),
+                                               _ptr(v_pages), _ptr(q_out), T, heads, kv_heads, dim, vdim, row, page_size,
+                                               _dtype_code(q_out), _stream()), "pair_rope_norm_store")
+    _count()
+    return q_out
+
+
+# ------------------------------------------------------------------------------------------ several outputs into the stream at once
+def sum_add_norm(x: torch.Tensor, terms, weight: Optional[torch.Tensor], kind: int, eps: float, out: Optional[torch.Tensor],
+                 rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """x float32 [T, H] += sum over ``terms`` (up to three) of scale * N(delta), each term a tuple (delta [T, H] in the
+    activation type, norm weight float32 [H] or None, norm kind NORM_NONE or NORM_RMS, eps, scale); then out = N(x) with
+    ``kind`` NORM_RMS (weight float32 [H]), NORM_COPY (x in the activation type) or NORM_NONE / ``out`` None (nothing).  With
+    ``rows`` (int32 [R]) out[r] is made from row rows[r] and x is left alone."""
+    terms = list(terms)
+    if len(terms) > 3:
+        raise KernelError("sum_add_norm: at most three terms")
+    H = x.shape[1]
+    R = rows.shape[0] if rows is not None else x.shape[0]
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("sum_add_norm: x must be contiguous float32 [T, H]")
+    like = out if out is not None else (terms[0][0] if terms else None)
+    if like is None:
+        return None
+    flat = []
+    for delta, w, k, e, s in terms:
+        _cuda(delta, w)
+        if delta.shape != x.shape or delta.dtype != like.dtype or not delta.is_contiguous():
+            raise KernelError("sum_add_norm: every term must be contiguous, shaped like x, in the activation type")
+        if k not in (NORM_NONE, NORM_RMS) or (w is not None and (w.dtype != torch.float32 or w.shape != (H,))):
+            raise KernelError("sum_add_norm: a term's norm is none or RMS with a float32 [H] weight")
+        flat += [_ptr(delta), _ptr(w), int(k), float(e), float(s)]
+    flat += [None, None, 0, 0.0, 0.0] * (3 - len(terms))
+    _cuda(x, weight, out, rows)
+    if weight is not None and (weight.dtype != torch.float32 or weight.shape != (H,)):
+        raise KernelError("sum_add_norm: weight must be float32 [H]")
+    if out is not None and (out.shape != (R, H) or not out.is_contiguous()):
+        raise KernelError("sum_add_norm: out must be contiguous [rows, H]")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("sum_add_norm: rows must be int32")
+    _check(library().pico_sum_add_norm(_ptr(x), *flat, _ptr(weight), int(kind) if out is not None else NORM_NONE, float(eps),
+                                       _ptr(out), _ptr(rows), R, H, _dtype_code(like), _stream()), f"sum_add_norm (width {H})")
+    _count()
+    return out
+
+
+def gelu_gate_rows(z: torch.Tensor, table: torch.Tensor, off: int, tokens: torch.Tensor,
+                   feedback: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """g[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], off + j] for z [T, n] (float32 inside; gelu_tanh(a) = a / 2 * (1 +
+    tanh(sqrt(2 / pi) (a + 0.044715 a^3)))).  A token id -(j + 1) names feedback[j], as in :func:`embedding`."""
+    _cuda(z, table, tokens, feedback)
+    T, n = z.shape
+    if not z.is_contiguous() or table.dim() != 2 or table.dtype != z.dtype or not table.is_contiguous() or off + n > table.shape[1]:
+        raise KernelError("gelu_gate_rows: z contiguous [T, n], table contiguous [V, >= off + n] of the same type")
+    if tokens.dtype != torch.int32 or tokens.shape[0] != T or (feedback is not None and feedback.dtype != torch.int32):
+        raise KernelError("gelu_gate_rows: tokens (and feedback) must be int32")
+    g = torch.empty_like(z)
+    _check(library().pico_gelu_gate_rows(_ptr(z), _ptr(table), table.stride(0), off, _ptr(tokens), _ptr(feedback), table.shape[0],
+                                         T, n, _ptr(g), _dtype_code(z), _stream()), "gelu_gate_rows")
+    _count()
+    return g
+
+
+def capped_glu(gu: torch.Tensor, ff: int, limit: float, row_gate_col: Optional[int] = None, alpha: float = 1.702) -> torch.Tensor:
+    """From rows [gate: ff | up: ff | ...]:  y = g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit,
+    limit), float32 inside; with ``row_gate_col`` the whole row is also multiplied by sigmoid of that column.  Returns [n, ff]."""
+    _cuda(gu)
+    if gu.dim() != 2 or gu.stride(1) != 1 or gu.shape[1] < 2 * ff or (row_gate_col is not None and not 0 <= row_gate_col < gu.shape[1]):
+        raise KernelError("capped_glu: rows must hold gate and up (and the row gate's column)")
+    out = torch.empty((gu.shape[0], ff), dtype=gu.dtype, device=gu.device)
+    _check(library().pico_capped_glu(_ptr(gu), gu.stride(0), gu.shape[0], ff, float(limit), float(alpha),
+                                     -1 if row_gate_col is None else int(row_gate_col), _ptr(out), _dtype_code(gu), _stream()),
+           "capped_glu")
+    _count()
+    return out

@@ -107,8 +107,13 @@ class ParallelMixers(Part):
     """Two mixers on the same input, left_scale * left(h) + right_scale * right(h).  Tensor keys of the two are prefixed
     ``left.`` and ``right.``; each keeps its own cache entries."""
 
-    def __init__(self, left: Part, right: Part, left_scale: float = 1.0, right_scale: float = 1.0):
+    def __init__(self, left: Part, right: Part, left_scale: float = 1.0, right_scale: float = 1.0,
+                 left_norm: Optional[Part] = None, right_norm: Optional[Part] = None):
+        """``left_norm`` / ``right_norm`` (RMS norms over the model width, tensor keys ``left.out`` / ``right.out``): each
+        side's output passes through its norm before the scaled sum; the mixer then hands back a
+        :class:`~pico_vllm_b200.parts.norm.SumDelta` and the sum happens where the residual stream is next touched."""
         self.left, self.right, self.left_scale, self.right_scale = left, right, float(left_scale), float(right_scale)
+        self.left_norm, self.right_norm = left_norm, right_norm
         self._n_left = len(_as_tuple(left.cache_spec()))
 
     def _sides(self):
@@ -120,10 +125,18 @@ class ParallelMixers(Part):
             for p in part.params():
                 out.append(Param(f"{name}__{p.attr}", tuple(Piece(f"{name}.{pc.key}", pc.shape) for pc in p.pieces),
                                  kind=p.kind, init=p.init))
+        for name, norm in (("left", self.left_norm), ("right", self.right_norm)):
+            if norm is not None:
+                for p in norm.params():
+                    out.append(Param(f"{name}norm__{p.attr}", tuple(Piece(f"{name}.out", pc.shape) for pc in p.pieces),
+                                     kind=p.kind, init=p.init))
         return out
 
     def assign(self, attr: str, tensor: torch.Tensor) -> None:
         side, _, inner = attr.partition("__")
+        if side in ("leftnorm", "rightnorm"):
+            getattr(self, side[:-4] + "_norm").assign(inner, tensor)
+            return
         getattr(self, side).assign(inner, tensor)
 
     def __getattr__(self, attr: str):
@@ -131,6 +144,8 @@ class ParallelMixers(Part):
         side, sep, inner = attr.partition("__")
         if sep and side in ("left", "right") and inner:
             return getattr(self.__dict__[side], inner)
+        if sep and side in ("leftnorm", "rightnorm") and inner:
+            return getattr(self.__dict__[side[:-4] + "_norm"], inner)
         raise AttributeError(attr)
 
     def cache_spec(self):
@@ -139,6 +154,9 @@ class ParallelMixers(Part):
     def materialize(self, device, dtype):
         self.left.materialize(device, dtype)
         self.right.materialize(device, dtype)
+        for norm in (self.left_norm, self.right_norm):
+            if norm is not None:
+                norm.materialize(device, dtype)
 
     def plan_key(self):
         return ("parallel_mixers", self.left.plan_key(), self.right.plan_key())
@@ -160,6 +178,9 @@ class ParallelMixers(Part):
             a = self.left.forward(h, batch, lv[0] if len(lv) == 1 else lv)
         with _side_plan(batch, self.right, None if own is None else own.right):
             b = self.right.forward(h, batch, rv[0] if len(rv) == 1 else rv)
+        if self.left_norm is not None or self.right_norm is not None:
+            from .norm import SumDelta
+            return SumDelta([(a, self.left_norm, self.left_scale), (b, self.right_norm, self.right_scale)])
         return ops.scaled_sum(a, self.left_scale, b, self.right_scale)
 
 

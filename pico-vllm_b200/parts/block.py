@@ -47,6 +47,39 @@ class PreNormBlock:
         return part.forward(h, *args)
 
 
+class ParallelBlock:
+    """A layer with ONE norm whose mixer and feed-forward both read its output and whose outputs are added together:
+    h = norm1(x); x += mixer(h) + feed_forward(h).  ``feed_forward`` may be None.  ``side`` (optional; a part with
+    ``read_norm``, ``forward(x_act, batch) -> delta`` and ``out_norm``): after that add, something made from the stream itself
+    and the batch's tokens passes through ``side.out_norm`` and is added too.  The adds are not done here: the outputs travel
+    on as one :class:`~pico_vllm_b200.parts.norm.SumDelta` (a mixer may hand back one of its own), the side's as a
+    :class:`~pico_vllm_b200.parts.norm.NormedDelta`, so that each add happens inside the kernel of whoever reads next."""
+
+    def __init__(self, norm1: Part, mixer: Part, feed_forward: Optional[Part] = None, side: Optional[Part] = None):
+        self.norm1, self.mixer, self.feed_forward, self.side = norm1, mixer, feed_forward, side
+
+    def parts(self):
+        p = {"norm1": self.norm1, "mixer": self.mixer}
+        if self.feed_forward is not None:
+            p["feed_forward"] = self.feed_forward
+        if self.side is not None:
+            p.update(side=self.side, side_norm=self.side.out_norm)
+        return p
+
+    def forward(self, x: torch.Tensor, pending, batch, cache: CacheView):
+        from .norm import NormedDelta, SumDelta
+        h = self.norm1.add_norm(x, pending)
+        a = self.mixer.forward(h, batch, cache)
+        terms = list(a.terms) if isinstance(a, SumDelta) else [(a, None, 1.0)]
+        if self.feed_forward is not None:
+            terms.append((self.feed_forward.forward(h, batch), None, 1.0))
+        delta = SumDelta(terms)
+        if self.side is None:
+            return x, delta
+        xa = self.side.read_norm.add_norm(x, delta)          # the adds, and the stream in the activation type
+        return x, NormedDelta(self.side.forward(xa, batch), self.side.out_norm)
+
+
 class SandwichBlock:
     """A layer that norms each sublayer's input and its output:  x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))).
     ``feed_forward`` (with ``norm2`` and ``norm2b``) may be None: the layer is then its mixer alone.  A sublayer's

@@ -17,8 +17,9 @@ from .base import Param, Part, Piece
 
 
 class TokenEmbedding(Part):
-    def __init__(self, vocab: int, width: int):
-        self.vocab, self.width = vocab, width
+    def __init__(self, vocab: int, width: int, scale: float = 1.0):
+        """``scale``: x = scale * E[ids], the product taken in float32 on the stream."""
+        self.vocab, self.width, self.scale = vocab, width, float(scale)
         self.weight = None
 
     def params(self) -> List[Param]:
@@ -26,7 +27,43 @@ class TokenEmbedding(Part):
 
     def forward(self, ids: torch.Tensor, feedback: Optional[torch.Tensor] = None) -> torch.Tensor:
         out = torch.empty((ids.shape[0], self.width), dtype=torch.float32, device=ids.device)
-        return ops.embedding(ids, self.weight, out, feedback)
+        ops.embedding(ids, self.weight, out, feedback)
+        return out if self.scale == 1.0 else ops.scale_add_rows(out, self.scale, None, None)
+
+
+class TokenSideTable(Part):
+    """A second embedding table whose row of a token is cut into one slice per layer (``parts`` slices of ``dim``)."""
+
+    def __init__(self, vocab: int, parts: int, dim: int):
+        self.vocab, self.parts_n, self.dim = vocab, parts, dim
+        self.weight = None
+
+    def params(self) -> List[Param]:
+        return [Param("weight", (Piece("weight", (self.vocab, self.parts_n * self.dim)),))]
+
+
+class TokenSideInput(Part):
+    """What a layer takes from the token itself, given the residual stream x (in the activation type) after the layer's
+    sublayers:  g = gelu_tanh(W_gate x) * e,  y = W_proj g,  with e slice ``index`` of the token's row of ``table``; y then
+    passes through ``out_norm`` (an RMS norm) on its way into the stream.  ``read_norm`` is how the block reads the stream
+    for this part: no norm, the pending adds done."""
+
+    def __init__(self, width: int, dim: int, index: int, table: TokenSideTable, out_norm: Part, read_norm: Part):
+        self.width, self.dim, self.index, self.table = width, dim, index, table
+        self.out_norm, self.read_norm = out_norm, read_norm
+        self.gate_weight = self.proj_weight = None
+
+    def params(self) -> List[Param]:
+        return [Param("gate_weight", (Piece("gate.weight", (self.dim, self.width)),)),
+                Param("proj_weight", (Piece("proj.weight", (self.width, self.dim)),))]
+
+    def materialize(self, device, dtype):
+        self.read_norm.materialize(device, dtype)
+
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        z = ops.linear(x, self.gate_weight)
+        g = ops.gelu_gate_rows(z, self.table.weight, self.index * self.dim, batch.token_ids, batch.feedback)
+        return ops.linear(g, self.proj_weight)
 
 
 class LearnedPositions(Part):

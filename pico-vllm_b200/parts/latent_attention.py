@@ -9,7 +9,9 @@ cached latent rank r:
     out = W_o concat_a( sigmoid(W_g h)_a * sum_j p_a(j) v_a(j) )
 
 No position encoding acts on q or k.  A layer may read the latents another layer caches (``own_latent=False``: it
-has no W_dkv; its cache entry is that layer's).
+has no W_dkv; its cache entry is that layer's).  Options: ``q_rank=None`` - the queries are projected directly, q = W_q h
+(no query latent, no norm on that side); ``gate=False`` - no output gate; ``window`` W - position i sees the last W
+positions, itself included.
 
 The kernels never expand k or v.  Since q_a . (W_uk[a] c) = (W_uk[a]^T q_a) . c, the query is carried into the
 latent space, q'_a = W_uk[a]^T q_a (r), attention runs over the cached latents as over ONE shared key/value head
@@ -46,26 +48,33 @@ def _linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 @register("mixer", "latent_attention")
 class LatentAttention(Part):
-    def __init__(self, width: int, heads: int, dim: int, vdim: int, q_rank: int, kv_rank: int, scale: float, eps: float,
-                 own_latent: bool = True, window: Optional[int] = None):
+    def __init__(self, width: int, heads: int, dim: int, vdim: int, q_rank: Optional[int], kv_rank: int, scale: float, eps: float,
+                 own_latent: bool = True, window: Optional[int] = None, gate: bool = True, cache_window="same"):
+        """``cache_window``: how many of the last latents the cache has to keep (None: all); by default the mixer's own
+        window.  Layers that read one cache entry through different windows all name the longest."""
         self.width, self.heads, self.dim, self.vdim = width, heads, dim, vdim
         self.q_rank, self.kv_rank, self.scale, self.eps = q_rank, kv_rank, float(scale), float(eps)
-        self.own_latent, self.window = own_latent, window
+        self.own_latent, self.window, self.gate = own_latent, window, gate
+        self.cache_window = window if cache_window == "same" else cache_window
         self.row = _round_up(kv_rank, 16)          # elements of a cache row: the attention kernels take multiples of 16
         self.down_weight = self.q_norm = self.kv_norm = self.uq_weight = self.uk_weight = self.uv_weight = None
         self.o_weight = None
 
     def params(self) -> List[Param]:
-        down = [Piece("dq.weight", (self.q_rank, self.width))]
+        down = [Piece("dq.weight", (self.q_rank, self.width))] if self.q_rank else []
         if self.own_latent:
             down.append(Piece("dkv.weight", (self.kv_rank, self.width)))
-        down.append(Piece("g.weight", (self.heads, self.width)))
-        ps = [Param("down_weight", tuple(down)),
-              Param("q_norm", (Piece("dq.norm", (self.q_rank,)),), kind="vector", init="one_plus_normal"),
-              Param("uq_weight", (Piece("uq.weight", (self.heads * self.dim, self.q_rank)),)),
-              Param("uk_weight", (Piece("uk.weight", (self.heads * self.dim, self.kv_rank)),)),
-              Param("uv_weight", (Piece("uv.weight", (self.heads * self.vdim, self.kv_rank)),)),
-              Param("o_weight", (Piece("o.weight", (self.width, self.heads * self.vdim)),))]
+        if self.gate:
+            down.append(Piece("g.weight", (self.heads, self.width)))
+        ps = [Param("down_weight", tuple(down))] if down else []
+        if self.q_rank:
+            ps += [Param("q_norm", (Piece("dq.norm", (self.q_rank,)),), kind="vector", init="one_plus_normal"),
+                   Param("uq_weight", (Piece("uq.weight", (self.heads * self.dim, self.q_rank)),))]
+        else:
+            ps.append(Param("uq_weight", (Piece("q.weight", (self.heads * self.dim, self.width)),)))
+        ps += [Param("uk_weight", (Piece("uk.weight", (self.heads * self.dim, self.kv_rank)),)),
+               Param("uv_weight", (Piece("uv.weight", (self.heads * self.vdim, self.kv_rank)),)),
+               Param("o_weight", (Piece("o.weight", (self.width, self.heads * self.vdim)),))]
         if self.own_latent:
             ps.append(Param("kv_norm", (Piece("dkv.norm", (self.kv_rank,)),), kind="vector", init="one_plus_normal"))
         return ps
@@ -89,7 +98,7 @@ class LatentAttention(Part):
         setattr(self, attr, tensor.contiguous())
 
     def cache_spec(self):
-        return PagedLatent(self.row, self.window)
+        return PagedLatent(self.row, self.cache_window)
 
     # ------------------------------------------------------------------ launch policy of the attention kernels
     def plan_key(self):
@@ -106,13 +115,18 @@ class LatentAttention(Part):
         T, H, R = h.shape[0], self.heads, self.row
         latent = cache.tensors["latent"]                       # [pages, 1, page_size, R]
         stores = self.own_latent and cache.store
-        proj = _linear(h, self.down_weight)
-        kv_off = self.q_rank
-        g_off = self.q_rank + (self.kv_rank if self.own_latent else 0)
-        cq, gate = ops.latent_norm_store(proj, 0, self.q_rank, self.q_norm, kv_off, self.kv_rank if stores else 0,
-                                         self.kv_norm if stores else None, gb.slots if stores else None,
-                                         latent if stores else None, g_off, H, self.eps)
-        q = _linear(cq, self.uq_weight)                         # [T, H d]
+        q_rank = self.q_rank or 0
+        cq, gate = h, None
+        if self.down_weight is not None:
+            proj = _linear(h, self.down_weight)
+            kv_off = q_rank
+            g_off = q_rank + (self.kv_rank if self.own_latent else 0)
+            cq, gate = ops.latent_norm_store(proj, 0, q_rank, self.q_norm, kv_off, self.kv_rank if stores else 0,
+                                             self.kv_norm if stores else None, gb.slots if stores else None,
+                                             latent if stores else None, g_off, H if self.gate else 0, self.eps)
+            if not q_rank:
+                cq = h
+        q = _linear(cq, self.uq_weight)                         # [T, H d]: from the query latent, or from h itself
         qa = torch.empty((T, H * R), dtype=h.dtype, device=h.device)
         ops.head_linear(q, self.uk_weight, qa)                  # q'_a = W_uk[a]^T q_a
         oa = torch.empty((T, H * R), dtype=h.dtype, device=h.device)

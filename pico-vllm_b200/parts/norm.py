@@ -27,6 +27,27 @@ class NormedDelta:
     norm: "Part"
 
 
+@dataclass
+class SumDelta:
+    """Several sublayer outputs that are still to be added to the residual stream together: ``terms`` is a list of
+    (delta, norm or None, scale) - each passes through its own norm (an RMS norm with a weight) or none and is multiplied
+    by ``scale`` on its way.  Up to three terms."""
+    terms: list
+
+    def flat(self):
+        return [(d, None if n is None else n.weight, ops.NORM_NONE if n is None else n.norm_kind, 0.0 if n is None else n.eps, s)
+                for d, n, s in self.terms]
+
+
+def _sum_add_norm(norm, kind: int, x: torch.Tensor, delta: "SumDelta", rows: Optional[torch.Tensor]) -> torch.Tensor:
+    if norm.act_dtype == torch.float32 and kind == ops.NORM_COPY and rows is None:
+        ops.sum_add_norm(x, delta.flat(), None, ops.NORM_NONE, 0.0, None)
+        return x                         # in float32 the stream itself is handed on (readers must not write to it)
+    n = rows.shape[0] if rows is not None else x.shape[0]
+    out = torch.empty((n, norm.width), dtype=norm.act_dtype, device=x.device)
+    return ops.sum_add_norm(x, delta.flat(), norm.weight, kind, norm.eps, out, rows)
+
+
 def _post_add_norm(norm, kind: int, x: torch.Tensor, delta, rows: Optional[torch.Tensor]) -> torch.Tensor:
     n = rows.shape[0] if rows is not None else x.shape[0]
     out = torch.empty((n, norm.width), dtype=norm.act_dtype, device=x.device)
@@ -72,6 +93,8 @@ class RMSNorm(Part):
             return streams_add_norm(self, x, delta, None, rows)
         if isinstance(delta, NormedDelta):
             return _post_add_norm(self, ops.NORM_RMS, x, delta, rows)
+        if isinstance(delta, SumDelta):
+            return _sum_add_norm(self, ops.NORM_RMS, x, delta, rows)
         n = rows.shape[0] if rows is not None else x.shape[0]
         out = torch.empty((n, self.width), dtype=self.act_dtype, device=x.device)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
@@ -135,6 +158,8 @@ class PassNorm(Part):
 
     def add_norm(self, x: torch.Tensor, delta: Union[None, torch.Tensor, NormedDelta],
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if isinstance(delta, SumDelta):
+            return _sum_add_norm(self, ops.NORM_COPY, x, delta, rows)
         if rows is None and self.act_dtype == torch.float32:
             post = None
             if isinstance(delta, NormedDelta):

@@ -51,6 +51,9 @@ def _register_builtin() -> None:
     from .config.zazilix import ZazilixConfig
     from .models.zazilix import build_zazilix
     register_architecture("Zazilix", ZazilixConfig, build_zazilix)
+    from .config.banazen import BanazenConfig
+    from .models.banazen import build_banazen
+    register_architecture("Banazen", BanazenConfig, build_banazen)
 
 
 _register_builtin()

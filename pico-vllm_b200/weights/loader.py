@@ -71,7 +71,7 @@ def check_tensors(model, have: Dict[str, Tuple[int, ...]], where: str) -> None:
     ignorable = getattr(model, "ignorable_tensors", set())
     missing = sorted(n for n in want if n not in have)
     unexpected = sorted(n for n in have if n not in want and n not in ignorable)
-    wrong = sorted((n, have[n], want[n]) for n in want if n in have and tuple(have[n]) != want[n])
+    wrong = sorted((n, have[n], want[n]) for n in want if n in have and not _fits(tuple(have[n]), want[n]))
     if not (missing or unexpected or wrong):
         return
     lines = [f"{where}: the tensors do not match the model"]
@@ -85,6 +85,11 @@ def check_tensors(model, have: Dict[str, Tuple[int, ...]], where: str) -> None:
     err = WeightError("\n".join(lines))
     err.missing, err.unexpected, err.wrong_shape = missing, unexpected, [w[0] for w in wrong]
     raise err
+
+
+def _fits(have: Tuple[int, ...], want: Tuple[int, ...]) -> bool:
+    """A wanted size of -1 is a size only the tensor gives (the part learns it when the tensor is assigned)."""
+    return len(have) == len(want) and all(w == -1 or h == w for h, w in zip(have, want))
 
 
 def _place(t: torch.Tensor, kind: str, mode: torch.dtype, name: str) -> torch.Tensor:

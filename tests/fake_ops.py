@@ -253,7 +253,7 @@ def scale_softcap(logits, scale, cap):
 
 def latent_norm_store(proj, q_off, q_rank, q_weight, kv_off, kv_rank, kv_weight, slots, cache, g_off, heads, eps):
     p = proj.float()
-    cq = _norm(p[:, q_off:q_off + q_rank], 1, q_weight, eps).to(proj.dtype)
+    cq = _norm(p[:, q_off:q_off + q_rank], 1, q_weight, eps).to(proj.dtype) if q_rank > 0 else None
     if kv_rank > 0:
         c = _norm(p[:, kv_off:kv_off + kv_rank], 1, kv_weight, eps).to(cache.dtype)
         flat = cache.view(-1, cache.shape[-1])
@@ -261,7 +261,7 @@ def latent_norm_store(proj, q_off, q_rank, q_weight, kv_off, kv_rank, kv_weight,
             if s >= 0:
                 flat[s].zero_()
                 flat[s, :kv_rank] = c[t]
-    return cq, torch.sigmoid(p[:, g_off:g_off + heads])
+    return cq, (torch.sigmoid(p[:, g_off:g_off + heads]) if heads > 0 else None)
 
 
 def head_linear(x, weight, out, gate=None):
@@ -280,14 +280,26 @@ def head_scale(o, gate, heads):
     return o
 
 
-def moe_route(h, router_weight, router_bias, top, scoring=0, choice_bias=None, weight_scale=1.0):
+def moe_route(h, router_weight, router_bias, top, scoring=0, choice_bias=None, weight_scale=1.0, groups=1, groups_keep=1,
+              renorm=False):
     z = h.float() @ router_weight.t()
     if router_bias is not None:
         z = z + router_bias
     if scoring == 2:
         score = torch.softmax(z, dim=-1)
-        idx = torch.topk(score + (choice_bias if choice_bias is not None else 0.0), top, dim=-1).indices
-        return idx.to(torch.int32), torch.gather(score, 1, idx) * weight_scale
+        choice = score + (choice_bias if choice_bias is not None else 0.0)
+        if groups > 1 and groups_keep < groups:
+            T, E = choice.shape
+            best = choice.view(T, groups, E // groups).max(-1).values
+            kept = torch.zeros(T, groups, dtype=torch.bool)
+            kept[torch.arange(T)[:, None], torch.topk(best, groups_keep, dim=-1).indices] = True
+            choice = torch.where(kept[:, :, None].expand(T, groups, E // groups).reshape(T, E), choice,
+                                 torch.full_like(choice, -math.inf))
+        idx = torch.topk(choice, top, dim=-1).indices
+        w = torch.gather(score, 1, idx)
+        if renorm:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        return idx.to(torch.int32), w * weight_scale
     val, idx = torch.topk(z, top, dim=-1)
     return idx.to(torch.int32), (torch.sigmoid(val) if scoring == 1 else torch.softmax(val, dim=-1))
 
@@ -296,7 +308,21 @@ def _act(u, act):
     return torch.relu(u) ** 2 if act == 1 else u * torch.sigmoid(u)
 
 
-def moe_experts(h, idx, wgt, gate_up_weight, down_weight, gated=True, act=0, weight_on_input=False, base=None, identity=0):
+def _capped(g, u, limit, alpha=1.702):
+    g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+    return g * torch.sigmoid(alpha * g) * (u + 1.0)
+
+
+def capped_glu(gu, ff, limit, row_gate_col=None, alpha=1.702):
+    x = gu.float()
+    y = _capped(x[:, :ff], x[:, ff:2 * ff], limit, alpha)
+    if row_gate_col is not None:
+        y = y * torch.sigmoid(x[:, row_gate_col:row_gate_col + 1])
+    return y.to(gu.dtype)
+
+
+def moe_experts(h, idx, wgt, gate_up_weight, down_weight, gated=True, act=0, weight_on_input=False, base=None, identity=0,
+                limit=0.0):
     ff = gate_up_weight.shape[1] // 2 if gated else gate_up_weight.shape[1]
     y = torch.zeros(h.shape, dtype=torch.float32) if base is None else base.float().clone()
     for t in range(h.shape[0]):
@@ -308,7 +334,7 @@ def moe_experts(h, idx, wgt, gate_up_weight, down_weight, gated=True, act=0, wei
             elif gated:
                 gu = gate_up_weight[e].float() @ h[t].float()
                 g, u = gu[:ff], gu[ff:]
-                y[t] += wgt[t, j] * (down_weight[e].float() @ (g * torch.sigmoid(g) * u))
+                y[t] += wgt[t, j] * (down_weight[e].float() @ (_capped(g, u, limit) if act == 2 else g * torch.sigmoid(g) * u))
             elif weight_on_input:
                 y[t] += down_weight[e].float() @ _act(gate_up_weight[e].float() @ (wgt[t, j] * h[t].float()), act)
             else:
@@ -468,7 +494,7 @@ def hgrn2_prepare(proj, q_off, f_off, v_off, f_bias, lower, nqk, nv):
     return torch.cat([q * torch.sigmoid(q), 1.0 - f, f, p[:, v_off:v_off + nv]], 1)
 
 
-def causal_conv_silu(proj, c_off, weight, bias, conv_state, tok_seg, seg_slots, cu_q, positions):
+def causal_conv_silu(proj, c_off, weight, bias, conv_state, tok_seg, seg_slots, cu_q, positions, act=True):
     C, taps = weight.shape
     T = proj.shape[0]
     out = torch.zeros(T, C)
@@ -480,7 +506,7 @@ def causal_conv_silu(proj, c_off, weight, bias, conv_state, tok_seg, seg_slots, 
         x = torch.cat([conv_state[slot], proj[a0:a1, c_off:c_off + C].float()])        # [taps - 1 + n, C]
         for t in range(a1 - a0):
             acc = (x[t:t + taps] * weight.t()).sum(0) + (bias if bias is not None else 0.0)
-            out[a0 + t] = acc * torch.sigmoid(acc)
+            out[a0 + t] = acc * torch.sigmoid(acc) if act else acc
         conv_state[slot] = x[x.shape[0] - (taps - 1):]
     return out
 
@@ -543,7 +569,108 @@ NAMES = ["hyper_expand", "hyper_step", "scale_add_rows", "scaled_sum", "gated_li
          "embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
          "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "make_kv_tensor_map_2d", "tc_takes", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
          "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
-         "linear", "logits_linear", "sample"]
+         "linear", "logits_linear", "sample", "delta_prepare", "gated_delta_rule", "pair_rope_norm_store", "sum_add_norm",
+         "gelu_gate_rows", "capped_glu"]
+
+
+def delta_prepare(xc, q_off, k_off, proj, b_off, dt, dt_bias, a_log, heads, kv_heads, dim, unit_eps=1e-6):
+    T, H, G, d = xc.shape[0], heads, kv_heads, dim
+    q = xc[:, q_off:q_off + G * d].reshape(T, G, d)
+    k = xc[:, k_off:k_off + G * d].reshape(T, G, d)
+    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * d ** -0.5
+    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+    z = dt.float() + (dt_bias if dt_bias is not None else 0.0)
+    keep = torch.exp(-torch.exp(a_log).repeat_interleave(d) * torch.nn.functional.softplus(z, threshold=20.0))
+    beta = torch.sigmoid(proj[:, b_off:b_off + H].float())
+    return torch.cat([q.reshape(T, -1), k.reshape(T, -1), keep, beta, (q * k).sum(-1)], 1).contiguous()
+
+
+def gated_delta_rule(prep, v, state, seg_slots, cu_q, positions, heads, kv_heads, dim, vdim):
+    T, H, G, d = prep.shape[0], heads, kv_heads, dim
+    q, k = prep[:, :G * d].reshape(T, G, d), prep[:, G * d:2 * G * d].reshape(T, G, d)
+    keep = prep[:, 2 * G * d:2 * G * d + H * d].reshape(T, H, d)
+    beta = prep[:, 2 * G * d + H * d:2 * G * d + H * d + H]
+    out = torch.zeros(T, H * vdim)
+    for s in range(seg_slots.shape[0]):
+        a0, a1 = int(cu_q[s]), int(cu_q[s + 1])
+        if a1 <= a0 or int(positions[a0]) < 0:
+            continue
+        slot = int(seg_slots[s])
+        for a in range(H):
+            g = a // (H // G)
+            S = state[slot, a].t().clone()                       # [d, vdim]
+            for t in range(a0, a1):
+                S = keep[t, a][:, None] * S
+                u = beta[t, a] * (v[t, a * vdim:(a + 1) * vdim] - S.t() @ k[t, g])
+                S = S + torch.outer(k[t, g], u)
+                out[t, a * vdim:(a + 1) * vdim] = S.t() @ q[t, g]
+            state[slot, a] = S.t()
+    return out
+
+
+def pair_rope_norm_store(x, q_off, k_off, v_off, positions, inv_freq, norm, q_w, k_w, eps, slots, k_pages, v_pages, heads,
+                         kv_heads, dim, vdim, row, page_size, out_dtype):
+    T = x.shape[0]
+    pos = positions.float().clamp(min=0)
+
+    def turn(t):                                                 # [T, n, dim]
+        t = t.clone()
+        if inv_freq is not None and inv_freq.numel():
+            r = inv_freq.shape[0]
+            ang = pos[:, None] * inv_freq[None, :]
+            c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            a, b = t[..., 0:2 * r:2].clone(), t[..., 1:2 * r:2].clone()
+            t[..., 0:2 * r:2] = a * c - b * s
+            t[..., 1:2 * r:2] = b * c + a * s
+        return t
+
+    def finish(t, w):
+        if norm:
+            t = t / torch.sqrt((t * t).mean(-1, keepdim=True) + eps)
+            if w is not None:
+                t = t * w
+        return torch.cat([t, t.new_zeros(t.shape[0], t.shape[1], row - dim)], -1)
+
+    q = finish(turn(x[:, q_off:q_off + heads * dim].reshape(T, heads, dim)), q_w)
+    k = finish(turn(x[:, k_off:k_off + kv_heads * dim].reshape(T, kv_heads, dim)), k_w)
+    v = x[:, v_off:v_off + kv_heads * vdim].reshape(T, kv_heads, vdim)
+    v = torch.cat([v, v.new_zeros(T, kv_heads, row - vdim)], -1)
+    if slots is not None:
+        for t, s in enumerate(slots.tolist()):
+            if s >= 0 and int(positions[t]) >= 0:
+                k_pages[s // page_size, :, s % page_size, :] = k[t].to(k_pages.dtype)
+                v_pages[s // page_size, :, s % page_size, :] = v[t].to(v_pages.dtype)
+    q = torch.where((positions >= 0)[:, None, None], q, torch.zeros_like(q))
+    return q.reshape(T, heads * row).to(out_dtype)
+
+
+def sum_add_norm(x, terms, weight, kind, eps, out, rows=None):
+    src = x if rows is None else x[rows.long()]
+    acc = src.clone()
+    for delta, w, k, e, s in terms:
+        d = (delta if rows is None else delta[rows.long()]).float()
+        if k == 1:
+            d = d / torch.sqrt((d * d).mean(-1, keepdim=True) + e)
+            if w is not None:
+                d = d * w
+        acc = acc + s * d
+    if rows is None:
+        x.copy_(acc)
+    if out is None or kind == 0:
+        return out
+    if kind == 1:
+        acc = acc / torch.sqrt((acc * acc).mean(-1, keepdim=True) + eps) * (weight if weight is not None else 1.0)
+    out.copy_(acc.to(out.dtype))
+    return out
+
+
+def gelu_gate_rows(z, table, off, tokens, feedback=None):
+    ids = tokens.long()
+    if feedback is not None:
+        ids = torch.where(ids < 0, feedback.long()[(-ids - 1).clamp(min=0)], ids)
+    a = z.float()
+    g = 0.5 * a * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (a + 0.044715 * a ** 3)))
+    return (g * table[ids.clamp(min=0), off:off + z.shape[1]].float()).to(z.dtype)
 
 
 def install(monkeypatch):
