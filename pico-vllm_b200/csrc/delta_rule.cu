@@ -10,9 +10,9 @@
 // delta_prepare_kernel makes the float32 inputs of the recurrence from the projections: q and k as unit vectors per head
 // (q times d^-1/2), beta = sigmoid, the decay a = exp(-exp(A_log) softplus(z + bias)) per head and row, and k . q.
 // gated_delta_rule_kernel is the recurrence: the columns of S evolve independently of each other, so a block takes
-// DR_WARPS * 4 columns of one head of one segment, a warp four of them, a lane the rows lane, lane + 32, ... in registers;
-// the state is stored transposed [slot, head, dv, d].  A token's q, k and decay pass through shared memory, DR_TOK tokens a
-// round, the next round's loads in flight (cp.async) while this one is walked.  A segment of one token is a decode step; a
+// DR_WARPS * 4 columns of one head of one segment, a warp four of them, eight lanes a column with the rows dealt out among
+// them in registers; the state is stored transposed [slot, head, dv, d].  A token's q, k and decay pass through shared
+// memory, DR_TOK tokens at a time, the next ones' loads in flight (cp.async) while these are walked.  A segment of one token is a decode step; a
 // portion of a prompt goes on from the state the portion before left.
 //
 // Everything here is float32 whatever the activation type; only the projections read are not.
@@ -98,34 +98,37 @@ __device__ __forceinline__ void dr_wait_all() { asm volatile("cp.async.wait_grou
 
 // prep: the rows delta_prepare_kernel wrote (q at 0, k at G d, a at 2 G d, beta and k . q after them); v float32 rows with
 // head h's values at h * dv; state float32 [slots, H, dv, d]; out float32 [T, H * dv].  Grid (column tiles, H, segments).
-template <int DPL>
+// A warp holds four columns, eight lanes each; lane l of a column holds the rows 4 l .. 4 l + 3, 32 + 4 l .., ... (RPL of
+// them), so a sum over rows is RPL multiply-adds in a lane (four chains side by side) and three exchanges among eight lanes: the
+// token-to-token chain - decay, two sums, write - is what sets this kernel's time, since tokens cannot run side by side.
+template <int RPL>
 __global__ void __launch_bounds__(DR_WARPS * 32)
 gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __restrict__ v, int v_stride,
                         float* __restrict__ state, const int* __restrict__ seg_slots, const int* __restrict__ cu_q,
                         const int* __restrict__ positions, float* __restrict__ out, int out_stride, int H, int G, int d,
                         int dv) {
-    pdl_launch_dependents();
+    // The kernel that follows is released at the end, not here: its blocks, resident and waiting beside this kernel's
+    // few warps, made the token loop 2.7 times slower (2.0 instead of 0.76 ms for 2,048 tokens).
     pdl_wait();
     extern __shared__ __align__(16) float dsm[];
-    const int dp = DPL * 32;
+    constexpr int dp = RPL * 8;
     constexpr int NC = DR_WARPS * DR_COLS;
-    // two buffers of DR_TOK tokens: q [dp], k [dp], a [dp], v [NC], beta, kq
-    const int tok_floats = 3 * dp + NC + 2;
+    // two buffers of DR_TOK tokens: q [dp], k [dp], a [dp], v [NC], beta, kq, and two floats that keep a token 16-byte aligned
+    constexpr int tok_floats = 3 * dp + NC + 4;
     const int seg = blockIdx.z, h = blockIdx.y, col_base = blockIdx.x * NC;
     const int t_begin = cu_q[seg], t_end = cu_q[seg + 1];
     if (t_end <= t_begin || positions[t_begin] < 0) return;      // an empty or a padding segment
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int col0 = col_base + warp * DR_COLS;
+    const int sub = lane & 7, cw = lane >> 3;                     // row lane and column of the warp
+    const int col = col_base + warp * DR_COLS + cw;
     const int hq = h / (H / G);
     float* st = state + ((size_t)seg_slots[seg] * H + h) * (size_t)dv * d;
-    float S[DPL][DR_COLS];
+    float S[RPL];
 #pragma unroll
-    for (int r = 0; r < DPL; ++r)
-#pragma unroll
-        for (int c = 0; c < DR_COLS; ++c) {
-            const int i = lane + 32 * r, j = col0 + c;
-            S[r][c] = (i < d && j < dv) ? st[(size_t)j * d + i] : 0.f;
-        }
+    for (int r = 0; r < RPL; ++r) {
+        const int i = 4 * sub + 32 * (r >> 2) + (r & 3);      // four neighbouring rows at a time: one 16-byte load a token
+        S[r] = (i < d && col < dv) ? st[(size_t)col * d + i] : 0.f;
+    }
     const int q_at = hq * d, k_at = G * d + hq * d, a_at = 2 * G * d + h * d, b_at = 2 * G * d + H * d + h,
               kq_at = 2 * G * d + H * d + H + hq;
     auto fetch = [&](int t0, int nt, float* buf) {
@@ -155,73 +158,65 @@ gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __re
         }
         dr_commit();
     };
-    float* bufs[2] = {dsm, dsm + DR_TOK * tok_floats};
-    fetch(t_begin, min(DR_TOK, t_end - t_begin), bufs[0]);
-    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
-    int round = 0;
-    for (int t0 = t_begin; t0 < t_end; t0 += DR_TOK, ++round) {
+    float* buf0 = dsm;
+    float* buf1 = dsm + DR_TOK * tok_floats;
+    fetch(t_begin, min(DR_TOK, t_end - t_begin), buf0);
+    int turn = 0;
+    for (int t0 = t_begin; t0 < t_end; t0 += DR_TOK, turn ^= 1) {
         const int nt = min(DR_TOK, t_end - t0);
         dr_wait_all();
-        __syncthreads();                    // this round's tokens are in; everyone is done with the other buffer
-        if (t0 + DR_TOK < t_end) fetch(t0 + DR_TOK, min(DR_TOK, t_end - t0 - DR_TOK), bufs[(round + 1) & 1]);
-        const float* buf = bufs[round & 1];
+        __syncthreads();                    // these tokens are in; everyone is done with the other buffer
+        if (t0 + DR_TOK < t_end) fetch(t0 + DR_TOK, min(DR_TOK, t_end - t0 - DR_TOK), turn ? buf0 : buf1);
+        const float* buf = turn ? buf1 : buf0;
+        float4 nq[RPL / 4], nk[RPL / 4], na[RPL / 4];      // the next token's rows, asked for a token ahead
+        auto rows_of = [&](int tt) {
+            const float* tk = buf + tt * tok_floats + 4 * sub;
+#pragma unroll
+            for (int j = 0; j < RPL / 4; ++j) {
+                nq[j] = *reinterpret_cast<const float4*>(tk + 32 * j);
+                nk[j] = *reinterpret_cast<const float4*>(tk + dp + 32 * j);
+                na[j] = *reinterpret_cast<const float4*>(tk + 2 * dp + 32 * j);
+            }
+        };
+        rows_of(0);
         for (int tt = 0; tt < nt; ++tt) {
             const float* tk = buf + tt * tok_floats;
-            float vals[2 * DR_COLS];
+            float p1[4] = {0.f, 0.f, 0.f, 0.f}, p2[4] = {0.f, 0.f, 0.f, 0.f};
+            float kr[RPL];
 #pragma unroll
-            for (int c = 0; c < 2 * DR_COLS; ++c) vals[c] = 0.f;
-            float kr[DPL];
+            for (int j = 0; j < RPL / 4; ++j) {
+                const float qv[4] = {nq[j].x, nq[j].y, nq[j].z, nq[j].w}, kv[4] = {nk[j].x, nk[j].y, nk[j].z, nk[j].w},
+                            av[4] = {na[j].x, na[j].y, na[j].z, na[j].w};
 #pragma unroll
-            for (int r = 0; r < DPL; ++r) {
-                const int i = lane + 32 * r;
-                const float qv = tk[i], kv = tk[dp + i], av = tk[2 * dp + i];
-                kr[r] = kv;
-#pragma unroll
-                for (int c = 0; c < DR_COLS; ++c) {
-                    const float s = S[r][c] * av;
-                    S[r][c] = s;
-                    vals[c] = fmaf(s, kv, vals[c]);
-                    vals[DR_COLS + c] = fmaf(s, qv, vals[DR_COLS + c]);
+                for (int e = 0; e < 4; ++e) {
+                    const int r = 4 * j + e;
+                    const float s = S[r] * av[e];
+                    kr[r] = kv[e];
+                    S[r] = s;
+                    p1[e] = fmaf(s, kv[e], p1[e]);
+                    p2[e] = fmaf(s, qv[e], p2[e]);
                 }
             }
-            // eight sums over the 32 lanes by halving: after the three exchanges a lane holds one of them, after two more
-            // steps its total; sum number 4 * bit4 + 2 * bit3 + bit2 of the lane
-            float a4[4], a2[2], a1;
+            if (tt + 1 < nt) rows_of(tt + 1);
+            float r1 = (p1[0] + p1[1]) + (p1[2] + p1[3]), r2 = (p2[0] + p2[1]) + (p2[2] + p2[3]);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                a4[i] = (b4 ? vals[i + 4] : vals[i]) + __shfl_xor_sync(0xffffffffu, b4 ? vals[i] : vals[i + 4], 16);
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-                a2[i] = (b3 ? a4[i + 2] : a4[i]) + __shfl_xor_sync(0xffffffffu, b3 ? a4[i] : a4[i + 2], 8);
-            a1 = (b2 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, b2 ? a2[0] : a2[1], 4);
-            a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
-            a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-            const float beta = tk[3 * dp + NC], kq = tk[3 * dp + NC + 1];
-            float u[DR_COLS];
-#pragma unroll
-            for (int c = 0; c < DR_COLS; ++c) {
-                const float r1 = __shfl_sync(0xffffffffu, a1, 8 * (c >> 1) + 4 * (c & 1));
-                u[c] = beta * (tk[3 * dp + warp * DR_COLS + c] - r1);
+            for (int o = 4; o > 0; o >>= 1) {
+                r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+                r2 += __shfl_xor_sync(0xffffffffu, r2, o);
             }
+            const float u = tk[3 * dp + NC] * (tk[3 * dp + warp * DR_COLS + cw] - r1);
 #pragma unroll
-            for (int r = 0; r < DPL; ++r)
-#pragma unroll
-                for (int c = 0; c < DR_COLS; ++c) S[r][c] = fmaf(kr[r], u[c], S[r][c]);
-            // the lanes 16 + 8 (c >> 1) + 4 (c & 1) hold r2 of column c
-            if (b4 && (lane & 3) == 0) {
-                const int c = ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                const float uc = c == 0 ? u[0] : c == 1 ? u[1] : c == 2 ? u[2] : u[3];
-                if (col0 + c < dv) out[(size_t)(t0 + tt) * out_stride + (size_t)h * dv + col0 + c] = fmaf(uc, kq, a1);
-            }
+            for (int r = 0; r < RPL; ++r) S[r] = fmaf(kr[r], u, S[r]);
+            if (sub == 0 && col < dv)
+                out[(size_t)(t0 + tt) * out_stride + (size_t)h * dv + col] = fmaf(u, tk[3 * dp + NC + 1], r2);
         }
     }
+    pdl_launch_dependents();
 #pragma unroll
-    for (int r = 0; r < DPL; ++r)
-#pragma unroll
-        for (int c = 0; c < DR_COLS; ++c) {
-            const int i = lane + 32 * r, j = col0 + c;
-            if (i < d && j < dv) st[(size_t)j * d + i] = S[r][c];
-        }
+    for (int r = 0; r < RPL; ++r) {
+        const int i = 4 * sub + 32 * (r >> 2) + (r & 3);
+        if (i < d && col < dv) st[(size_t)col * d + i] = S[r];
+    }
 }
 
 PICO_API int pico_gated_delta_rule(const float* prep, const float* v, int v_stride, float* state, const int* seg_slots,
@@ -230,21 +225,26 @@ PICO_API int pico_gated_delta_rule(const float* prep, const float* v, int v_stri
     if (S <= 0) return 0;
     if (H < 1 || G < 1 || H % G || d < 1 || d > 256 || dv < 1) return PICO_ERR_SIZE;
     const int P = 2 * G * d + H * d + H + G;
-    const int dpl = (d + 31) / 32;
+    const int rpl = (d + 7) / 8;
     const dim3 grid((dv + DR_WARPS * DR_COLS - 1) / (DR_WARPS * DR_COLS), H, S);
     if (grid.z > 65535 || grid.y > 65535) return PICO_ERR_SIZE;
+    // A grid that fits on the device one block to a multiprocessor asks for more shared memory than half of one, so that
+    // no two blocks share a multiprocessor: released early behind a kernel that is still draining, the blocks of a
+    // 2,048-token prompt landed four to a multiprocessor on the first ones that had room and took 1.5 ms instead of 0.8.
+    const bool alone = (long long)grid.x * grid.y * grid.z <= pico_num_sms();
 #define DR_LAUNCH(N)                                                                                                        \
     do {                                                                                                                    \
-        const size_t smem = (size_t)2 * DR_TOK * (3 * N * 32 + DR_WARPS * DR_COLS + 2) * sizeof(float);                     \
+        size_t smem = (size_t)2 * DR_TOK * (3 * N * 8 + DR_WARPS * DR_COLS + 4) * sizeof(float);                            \
+        if (alone && smem < 116 * 1024) smem = 116 * 1024;                                                                  \
         if (smem > 48 * 1024)                                                                                               \
             cudaFuncSetAttribute(gated_delta_rule_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
         pico_launch((gated_delta_rule_kernel<N>), grid, dim3(DR_WARPS * 32), smem, stream, prep, P, v, v_stride, state,     \
                     seg_slots, cu_q, positions, out, out_stride, H, G, d, dv);                                              \
     } while (0)
-    if (dpl <= 1) DR_LAUNCH(1);
-    else if (dpl <= 2) DR_LAUNCH(2);
-    else if (dpl <= 4) DR_LAUNCH(4);
-    else DR_LAUNCH(8);
+    if (rpl <= 4) DR_LAUNCH(4);
+    else if (rpl <= 8) DR_LAUNCH(8);
+    else if (rpl <= 16) DR_LAUNCH(16);
+    else DR_LAUNCH(32);
 #undef DR_LAUNCH
     return pico_launch_status();
 }

@@ -150,6 +150,36 @@ __global__ void capped_glu_kernel(const TA* __restrict__ gu, int row_stride, int
     }
 }
 
+// bfloat16 rows whose parts start at multiples of 8 elements: 16 bytes per access.
+__global__ void capped_glu_bf16x8_kernel(const bf16* __restrict__ gu, int row_stride, int ff8, float limit, float alpha,
+                                         int row_gate_col, size_t total8, bf16* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = idx / ff8;
+        const int j = (int)(idx - p * ff8) * 8;
+        const bf16* row = gu + p * row_stride;
+        const uint4 graw = *reinterpret_cast<const uint4*>(row + j);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(row + ff8 * 8 + j);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+        const float rg = row_gate_col >= 0 ? 1.0f / (1.0f + expf(-to_f32(row[row_gate_col]))) : 1.0f;
+        uint4 res;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+            g.x = fminf(g.x, limit);
+            g.y = fminf(g.y, limit);
+            u.x = fminf(fmaxf(u.x, -limit), limit);
+            u.y = fminf(fmaxf(u.y, -limit), limit);
+            o2[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-alpha * g.x)) * (u.x + 1.0f) * rg,
+                                          g.y / (1.0f + expf(-alpha * g.y)) * (u.y + 1.0f) * rg);
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = res;
+    }
+}
+
 PICO_API int pico_capped_glu(const void* gu, int row_stride, int n, int ff, float limit, float alpha, int row_gate_col, void* out,
                              int dtype, cudaStream_t stream) {
     if (n <= 0 || ff <= 0) return 0;
@@ -157,6 +187,12 @@ PICO_API int pico_capped_glu(const void* gu, int row_stride, int n, int ff, floa
     const long long cap = 16LL * pico_num_sms();
     const size_t want = (total + 255) / 256;
     const int blocks = (int)((long long)want > cap ? cap : (long long)want);
+    if (dtype == PICO_BF16 && ff % 8 == 0 && row_stride % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        const size_t want8 = (total / 8 + 255) / 256;
+        pico_launch(capped_glu_bf16x8_kernel, dim3((int)((long long)want8 > cap ? cap : (long long)want8)), dim3(256), 0, stream,
+                    (const bf16*)gu, row_stride, ff / 8, limit, alpha, row_gate_col, total / 8, (bf16*)out);
+        return pico_launch_status();
+    }
     if (dtype == PICO_F32)
         pico_launch((capped_glu_kernel<float>), dim3(blocks), dim3(256), 0, stream, (const float*)gu, row_stride, ff, limit, alpha,
                     row_gate_col, total, (float*)out);

@@ -78,8 +78,12 @@ class GatedDeltaRule(Part):
         self.decay_rank, self.gate_rank = self.a1_weight.shape[0], self.g1_weight.shape[0]
         if len({p.dtype for p in parts}) > 1:
             parts = [p.to(torch.float32) for p in parts]
+        n0, n1, n2 = self.qkvb_weight.shape[0], self.decay_rank, self.gate_rank
         self.proj_weight = torch.cat(parts, 0).contiguous()
-        self.qkvb_weight = self.a1_weight = self.g1_weight = None
+        # the three parameters live on as rows of the one matrix
+        self.qkvb_weight = self.proj_weight[:n0]
+        self.a1_weight = self.proj_weight[self.a1_off:self.a1_off + n1]
+        self.g1_weight = self.proj_weight[self.g1_off:self.g1_off + n2]
 
     def cache_spec(self):
         return (FixedState((self.heads, self.vdim, self.dim), "float32"),

@@ -293,7 +293,7 @@ def test_token_gate_and_capped_activation(dtype):
     tol = 2e-6 if dtype == torch.float32 else 1e-2
     _close(ops.gelu_gate_rows(z.to(DEV), table.to(DEV), 2 * n + 1, ids.to(DEV), fb.to(DEV)),
            fake_ops.gelu_gate_rows(z, table, 2 * n + 1, ids, fb), tol, "token gate")
-    for ff, limit, col in ((12, 0.7, None), (20, 2.0, 40), (7, 1.0, 15)):
+    for ff, limit, col in ((12, 0.7, None), (20, 2.0, 40), (7, 1.0, 15), (24, 1.3, 48), (64, 0.5, None)):
         gu = (torch.randn(T, 2 * ff + 8, generator=g) * 2).to(dtype)
         _close(ops.capped_glu(gu.to(DEV), ff, limit, col), fake_ops.capped_glu(gu, ff, limit, col), tol, "capped activation")
 
