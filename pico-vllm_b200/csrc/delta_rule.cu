@@ -10,8 +10,8 @@
 // delta_prepare_kernel makes the float32 inputs of the recurrence from the projections: q and k as unit vectors per head
 // (q times d^-1/2), beta = sigmoid, the decay a = exp(-exp(A_log) softplus(z + bias)) per head and row, and k . q.
 // gated_delta_rule_kernel is the recurrence: the columns of S evolve independently of each other, so a block takes
-// DR_WARPS * 4 columns of one head of one segment, a warp four of them, eight lanes a column with the rows dealt out among
-// them in registers; the state is stored transposed [slot, head, dv, d].  A token's q, k and decay pass through shared
+// 16 columns of one head of one segment, eight or sixteen lanes a column with the rows dealt out among them in
+// registers; the state is stored transposed [slot, head, dv, d].  A token's q, k and decay pass through shared
 // memory, DR_TOK tokens at a time, the next ones' loads in flight (cp.async) while these are walked.  A segment of one token is a decode step; a
 // portion of a prompt goes on from the state the portion before left.
 //
@@ -19,8 +19,6 @@
 #include "common.cuh"
 
 #define DR_TOK 8
-#define DR_WARPS 4
-#define DR_COLS 4
 
 __device__ __forceinline__ float dr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float dr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -98,11 +96,11 @@ __device__ __forceinline__ void dr_wait_all() { asm volatile("cp.async.wait_grou
 
 // prep: the rows delta_prepare_kernel wrote (q at 0, k at G d, a at 2 G d, beta and k . q after them); v float32 rows with
 // head h's values at h * dv; state float32 [slots, H, dv, d]; out float32 [T, H * dv].  Grid (column tiles, H, segments).
-// A warp holds four columns, eight lanes each; lane l of a column holds the rows 4 l .. 4 l + 3, 32 + 4 l .., ... (RPL of
-// them), so a sum over rows is RPL multiply-adds in a lane (four chains side by side) and three exchanges among eight lanes: the
+// A column is held by LPC lanes of a warp; lane l of a column holds the rows 4 l .. 4 l + 3, 4 LPC + 4 l .., ... (RPL of
+// them), so a sum over rows is RPL multiply-adds in a lane (four chains side by side) and log2(LPC) exchanges among the lanes: the
 // token-to-token chain - decay, two sums, write - is what sets this kernel's time, since tokens cannot run side by side.
-template <int RPL>
-__global__ void __launch_bounds__(DR_WARPS * 32)
+template <int RPL, int LPC>      // rows a lane, lanes a column (8 or 16): a block holds 16 columns in 16 * LPC threads
+__global__ void __launch_bounds__(16 * LPC)
 gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __restrict__ v, int v_stride,
                         float* __restrict__ state, const int* __restrict__ seg_slots, const int* __restrict__ cu_q,
                         const int* __restrict__ positions, float* __restrict__ out, int out_stride, int H, int G, int d,
@@ -111,28 +109,28 @@ gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __re
     // few warps, made the token loop 2.7 times slower (2.0 instead of 0.76 ms for 2,048 tokens).
     pdl_wait();
     extern __shared__ __align__(16) float dsm[];
-    constexpr int dp = RPL * 8;
-    constexpr int NC = DR_WARPS * DR_COLS;
+    constexpr int dp = RPL * LPC;
+    constexpr int NC = 16, CPW = 32 / LPC, NTH = 16 * LPC;
     // two buffers of DR_TOK tokens: q [dp], k [dp], a [dp], v [NC], beta, kq, and two floats that keep a token 16-byte aligned
     constexpr int tok_floats = 3 * dp + NC + 4;
     const int seg = blockIdx.z, h = blockIdx.y, col_base = blockIdx.x * NC;
     const int t_begin = cu_q[seg], t_end = cu_q[seg + 1];
     if (t_end <= t_begin || positions[t_begin] < 0) return;      // an empty or a padding segment
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int sub = lane & 7, cw = lane >> 3;                     // row lane and column of the warp
-    const int col = col_base + warp * DR_COLS + cw;
+    const int sub = lane % LPC, cw = lane / LPC;                  // row lane and column of the warp
+    const int col = col_base + warp * CPW + cw;
     const int hq = h / (H / G);
     float* st = state + ((size_t)seg_slots[seg] * H + h) * (size_t)dv * d;
     float S[RPL];
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
-        const int i = 4 * sub + 32 * (r >> 2) + (r & 3);      // four neighbouring rows at a time: one 16-byte load a token
+        const int i = 4 * sub + 4 * LPC * (r >> 2) + (r & 3);  // four neighbouring rows at a time: one 16-byte load a token
         S[r] = (i < d && col < dv) ? st[(size_t)col * d + i] : 0.f;
     }
     const int q_at = hq * d, k_at = G * d + hq * d, a_at = 2 * G * d + h * d, b_at = 2 * G * d + H * d + h,
               kq_at = 2 * G * d + H * d + H + hq;
     auto fetch = [&](int t0, int nt, float* buf) {
-        for (int idx = threadIdx.x; idx < nt * dp; idx += DR_WARPS * 32) {
+        for (int idx = threadIdx.x; idx < nt * dp; idx += NTH) {
             const int tt = idx / dp, i = idx - tt * dp;
             float* dst = buf + tt * tok_floats;
             if (i < d) {
@@ -146,7 +144,7 @@ gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __re
                 dst[2 * dp + i] = 1.f;
             }
         }
-        for (int idx = threadIdx.x; idx < nt * (NC + 2); idx += DR_WARPS * 32) {
+        for (int idx = threadIdx.x; idx < nt * (NC + 2); idx += NTH) {
             const int tt = idx / (NC + 2), c = idx - tt * (NC + 2);
             float* dst = buf + tt * tok_floats + 3 * dp;
             const float* src = prep + (size_t)(t0 + tt) * P;
@@ -173,9 +171,9 @@ gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __re
             const float* tk = buf + tt * tok_floats + 4 * sub;
 #pragma unroll
             for (int j = 0; j < RPL / 4; ++j) {
-                nq[j] = *reinterpret_cast<const float4*>(tk + 32 * j);
-                nk[j] = *reinterpret_cast<const float4*>(tk + dp + 32 * j);
-                na[j] = *reinterpret_cast<const float4*>(tk + 2 * dp + 32 * j);
+                nq[j] = *reinterpret_cast<const float4*>(tk + 4 * LPC * j);
+                nk[j] = *reinterpret_cast<const float4*>(tk + dp + 4 * LPC * j);
+                na[j] = *reinterpret_cast<const float4*>(tk + 2 * dp + 4 * LPC * j);
             }
         };
         rows_of(0);
@@ -200,11 +198,11 @@ gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __re
             if (tt + 1 < nt) rows_of(tt + 1);
             float r1 = (p1[0] + p1[1]) + (p1[2] + p1[3]), r2 = (p2[0] + p2[1]) + (p2[2] + p2[3]);
 #pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
+            for (int o = LPC / 2; o > 0; o >>= 1) {
                 r1 += __shfl_xor_sync(0xffffffffu, r1, o);
                 r2 += __shfl_xor_sync(0xffffffffu, r2, o);
             }
-            const float u = tk[3 * dp + NC] * (tk[3 * dp + warp * DR_COLS + cw] - r1);
+            const float u = tk[3 * dp + NC] * (tk[3 * dp + warp * CPW + cw] - r1);
 #pragma unroll
             for (int r = 0; r < RPL; ++r) S[r] = fmaf(kr[r], u, S[r]);
             if (sub == 0 && col < dv)
@@ -214,7 +212,7 @@ gated_delta_rule_kernel(const float* __restrict__ prep, int P, const float* __re
     pdl_launch_dependents();
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
-        const int i = 4 * sub + 32 * (r >> 2) + (r & 3);
+        const int i = 4 * sub + 4 * LPC * (r >> 2) + (r & 3);
         if (i < d && col < dv) st[(size_t)col * d + i] = S[r];
     }
 }
@@ -225,26 +223,27 @@ PICO_API int pico_gated_delta_rule(const float* prep, const float* v, int v_stri
     if (S <= 0) return 0;
     if (H < 1 || G < 1 || H % G || d < 1 || d > 256 || dv < 1) return PICO_ERR_SIZE;
     const int P = 2 * G * d + H * d + H + G;
-    const int rpl = (d + 7) / 8;
-    const dim3 grid((dv + DR_WARPS * DR_COLS - 1) / (DR_WARPS * DR_COLS), H, S);
+    const dim3 grid((dv + 15) / 16, H, S);
     if (grid.z > 65535 || grid.y > 65535) return PICO_ERR_SIZE;
     // A grid that fits on the device one block to a multiprocessor asks for more shared memory than half of one, so that
     // no two blocks share a multiprocessor: released early behind a kernel that is still draining, the blocks of a
     // 2,048-token prompt landed four to a multiprocessor on the first ones that had room and took 1.5 ms instead of 0.8.
     const bool alone = (long long)grid.x * grid.y * grid.z <= pico_num_sms();
-#define DR_LAUNCH(N)                                                                                                        \
+#define DR_LAUNCH(N, L)                                                                                                     \
     do {                                                                                                                    \
-        size_t smem = (size_t)2 * DR_TOK * (3 * N * 8 + DR_WARPS * DR_COLS + 4) * sizeof(float);                            \
+        size_t smem = (size_t)2 * DR_TOK * (3 * N * L + 16 + 4) * sizeof(float);                                            \
         if (alone && smem < 116 * 1024) smem = 116 * 1024;                                                                  \
         if (smem > 48 * 1024)                                                                                               \
-            cudaFuncSetAttribute(gated_delta_rule_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        pico_launch((gated_delta_rule_kernel<N>), grid, dim3(DR_WARPS * 32), smem, stream, prep, P, v, v_stride, state,     \
+            cudaFuncSetAttribute(gated_delta_rule_kernel<N, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        pico_launch((gated_delta_rule_kernel<N, L>), grid, dim3(16 * L), smem, stream, prep, P, v, v_stride, state,         \
                     seg_slots, cu_q, positions, out, out_stride, H, G, d, dv);                                              \
     } while (0)
-    if (rpl <= 4) DR_LAUNCH(4);
-    else if (rpl <= 8) DR_LAUNCH(8);
-    else if (rpl <= 16) DR_LAUNCH(16);
-    else DR_LAUNCH(32);
+    // keys of up to 32: eight lanes a column (four warps a block); longer keys: sixteen (eight warps), so that a
+    // multiprocessor's four schedulers each have two warps to choose from
+    if (d <= 32) DR_LAUNCH(4, 8);
+    else if (d <= 64) DR_LAUNCH(4, 16);
+    else if (d <= 128) DR_LAUNCH(8, 16);
+    else DR_LAUNCH(16, 16);
 #undef DR_LAUNCH
     return pico_launch_status();
 }
