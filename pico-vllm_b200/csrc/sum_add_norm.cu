@@ -28,27 +28,31 @@ __global__ void sum_add_norm_kernel(float* __restrict__ x, SumTerm t0, SumTerm t
                                     int kind, float eps, TA* __restrict__ out, const int* __restrict__ rows, int H) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ __align__(16) float sm[];      // acc [H], term [H], 33 of scratch
+    extern __shared__ __align__(16) float sm[];      // the stream's row and the three terms' rows [4][H], 33 of scratch
     float* acc = sm;
-    float* cur = sm + H;
-    float* scratch = cur + H;
+    float* scratch = sm + 4 * (size_t)H;
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) acc[i] = x[src + i];
     const SumTerm terms[3] = {t0, t1, t2};
+    // every load of the row - the stream and all terms - is issued before anything is waited for
+    float ss[3] = {0.f, 0.f, 0.f};
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        acc[i] = x[src + i];
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+            if (terms[k].delta) {
+                const float v = to_f32(((const TA*)terms[k].delta)[src + i]);
+                acc[(k + 1) * (size_t)H + i] = v;
+                ss[k] = fmaf(v, v, ss[k]);
+            }
+    }
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
         const SumTerm tm = terms[k];
         if (!tm.delta) continue;
-        const TA* d = (const TA*)tm.delta + src;
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float v = to_f32(d[i]);
-            cur[i] = v;
-            ss = fmaf(v, v, ss);
-        }
         float inv = tm.scale;
-        if (tm.kind == SAN_RMS) inv *= 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + tm.eps);
+        if (tm.kind == SAN_RMS) inv *= 1.0f / sqrtf(block_sum(ss[k], scratch) / (float)H + tm.eps);
+        const float* cur = acc + (k + 1) * (size_t)H;
         for (int i = threadIdx.x; i < H; i += blockDim.x) acc[i] += cur[i] * inv * (tm.kind == SAN_RMS && tm.w ? tm.w[i] : 1.0f);
     }
     if (!rows)
@@ -56,9 +60,9 @@ __global__ void sum_add_norm_kernel(float* __restrict__ x, SumTerm t0, SumTerm t
     if (!out || kind == SAN_NONE) return;
     float inv = 1.0f;
     if (kind == SAN_RMS) {
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < H; i += blockDim.x) ss = fmaf(acc[i], acc[i], ss);
-        inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
+        float s2 = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) s2 = fmaf(acc[i], acc[i], s2);
+        inv = 1.0f / sqrtf(block_sum(s2, scratch) / (float)H + eps);
     }
     TA* dst = out + (size_t)r * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = from_f32<TA>(kind == SAN_RMS ? acc[i] * inv * (w ? w[i] : 1.0f) : acc[i]);
@@ -74,9 +78,9 @@ PICO_API int pico_sum_add_norm(float* x, const void* d0, const float* w0, int k0
     for (int k : {k0, k1, k2})
         if (k != SAN_NONE && k != SAN_RMS) return PICO_ERR_SIZE;
     if (kind != SAN_NONE && kind != SAN_RMS && kind != SAN_COPY) return PICO_ERR_SIZE;
-    const size_t smem = (size_t)(2 * H + 33) * sizeof(float);
+    const size_t smem = (size_t)(4 * (size_t)H + 33) * sizeof(float);
     if (smem > 200 * 1024) return PICO_ERR_SIZE;
-    const int threads = H <= 256 ? 64 : H <= 1024 ? 128 : 256;
+    const int threads = H <= 256 ? 64 : H <= 512 ? 128 : 256;
     const SumTerm a = {d0, w0, k0, e0, s0}, b = {d1, w1, k1, e1, s1}, c = {d2, w2, k2, e2, s2};
 #define SAN_LAUNCH(TA)                                                                                                     \
     do {                                                                                                                   \
