@@ -382,6 +382,67 @@ def test_every_cutting_matches_plain(dtype, name, cut, graph):
     _status()
 
 
+def _random_shape(seed):
+    """A model whose every size, count, constant and order of layers is drawn from ``seed``."""
+    import random
+    rnd = random.Random(seed)
+    pick = rnd.choice
+    width = pick([64, 72, 96, 160, 320])
+    n = rnd.randint(3, 6)
+    layers, makers = [], []                   # makers: layers that make their own latents (index, rank)
+    for i in range(n):
+        kind = pick(["parallel", "latent", "latent", "from"]) if makers else pick(["parallel", "latent"])
+        if kind == "parallel":
+            G = pick([1, 2, 3])
+            H = G * pick([1, 2, 3])
+            d, dv = pick([16, 32, 64, 24]), pick([16, 32, 64, 40])
+            rot = None if rnd.random() < 0.15 else (pick([100.0, 10000.0, 500000.0]), pick([d, d // 2, 8]))
+            G2 = pick([1, 2, 4])
+            right = (G2 * pick([1, 2]), G2, pick([16, 32, 64, 48]), pick([16, 32, 64, 24]), rnd.randint(1, 4), rnd.randint(2, 12),
+                     rnd.randint(2, 12))
+            mixer = _par((H, G, d, dv, pick([0.125, 0.2, d ** -0.5]), rnd.randint(1, 4), rot), right)
+        else:
+            window = pick([None, 5, 16, 33, 72, 100])
+            H, d, dv = rnd.randint(1, 8), pick([16, 32, 64, 24]), pick([16, 32, 64, 8])
+            if kind == "from":
+                src, rank = pick(makers)
+                mixer = _lat(H, d, dv, rank, pick([0.125, 0.3]), window, kv_from=src)
+            else:
+                rank = pick([32, 64, 96, 128, 40])
+                makers.append((i, rank))
+                mixer = _lat(H, d, dv, rank, pick([0.125, 0.3]), window)
+        f = rnd.random()
+        if f < 0.15:
+            mlp = None
+        elif f < 0.35:
+            mlp = _dense(pick([48, 64, 100, 384]))
+        else:
+            count = pick([1, 2, 4])
+            per = pick([1, 2, 4])
+            keep = rnd.randint(1, count)
+            top = rnd.randint(1, min(per * keep, 6))
+            shared = None if rnd.random() < 0.3 else (pick([16, 40, 96]), pick([0.5, 1.0, 3.0]))
+            mlp = _moe(pick([16, 24, 64]), pick([0.7, 2.0, 6.0]), count * per, top, (count, keep), pick([1.0, 2.5, 0.6]), shared)
+        layers.append(_layer(mixer, mlp))
+    return _model(pick([97, 211, 448, 1000]), width, layers, side=pick([None, 4, 24, 9]), eps=pick([1e-5, 1e-6, 1e-4]),
+                  emb=pick([1.0, width ** 0.5, 0.3]), logit_scale=pick([1.0, 0.5, 2.0]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_drawn_shapes_in_mixed_batches(dtype, seed):
+    """Eight models drawn at random - sizes, head counts, order of layers, windows, taps, groups, constants - each with four
+    live requests, portions beside single tokens, pages and slots used again, against the plain implementation."""
+    raw = _raw(_random_shape(seed), dtype)
+    tensors = _tensors(raw, 100 + seed)
+    reqs = {f"r{i}": helpers.random_ids(n, raw["vocab"], 40 * seed + i) for i, n in enumerate([150, 3, 41, 77, 120, 18])}
+    steps = helpers.trace_mixed(reqs, max_live=4, seed=seed)
+    runner = _runner(raw, tensors, dtype, helpers.live_token_peak(steps), graph=seed % 2 == 0)
+    _compare(steps, reqs, helpers.replay(runner, steps), _oracle(raw, tensors, reqs), dtype, f"drawn {seed}/{dtype}")
+    assert all(g.pool.in_use == 0 for g in runner.cache.groups)
+    _status()
+
+
 ALONE = {
     "latent": [_layer(_lat(3, 24, 40, 56, 0.3, window=20), None)],
     "shared latent": [_layer(_lat(2, 16, 16, 24, 0.3), None), _layer(_lat(4, 8, 24, 24, 0.4, window=11, kv_from=0), None)],
