@@ -445,6 +445,7 @@ def test_drawn_shapes_in_mixed_batches(dtype, seed):
 
 ALONE = {
     "latent": [_layer(_lat(3, 24, 40, 56, 0.3, window=20), None)],
+    "many heads": [_layer(_lat(20, 16, 16, 32, 0.3, window=30), None), _layer(_lat(16, 24, 8, 32, 0.3, kv_from=0), None)],
     "shared latent": [_layer(_lat(2, 16, 16, 24, 0.3), None), _layer(_lat(4, 8, 24, 24, 0.4, window=11, kv_from=0), None)],
     "pair": [_layer(_par((4, 2, 32, 16, 0.4, 3, (1000.0, 20)), (3, 1, 24, 40, 4, 4, 6)), None)],
     "dense": [_layer(_lat(1, 8, 8, 16, 0.3), _dense(44))],
