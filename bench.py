@@ -794,7 +794,7 @@ def main():
                     help="run one phase only and print a short line (for profiling; not a bench value)")
     ap.add_argument("--design", choices=["zapipel", "zikupel", "zazilix", "banazen"], default=None,
                     help="the named design beside the closest earlier model at equal sizes (zapipel, zikupel: the Qwen2 decoder; "
-                         "zazilix: zikupel), prefill and decode; not the default run")
+                         "zazilix: zikupel; banazen: zazilix), prefill and decode; not the default run")
     ap.add_argument("--shape", choices=sorted(DESIGN_SHAPES) + ["all"], default="all", help="with --design: which sizes")
     ap.add_argument("--arch", choices=["zapipel", "zikupel", "zazilix", "banazen", "qwen2", "both"], default="both",
                     help="with --design: which model (both: the design and the model it is measured beside)")
