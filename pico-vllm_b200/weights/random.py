@@ -15,6 +15,7 @@ from typing import Dict
 import numpy as np
 import torch
 
+from ..errors import ConfigError
 from ..registry import build_model
 
 
@@ -30,7 +31,7 @@ def random_tensors(config, seed: int, std: float = 0.02, dtype: torch.dtype = to
     def draw(job):
         idx, (name, shape, init) = job
         if any(n < 0 for n in shape):
-            raise ValueError(f"{name}: a size that only a tensor gives must be set in the configuration to draw random weights")
+            raise ConfigError(f"{name}: a size that only a tensor gives must be set in the configuration to draw random weights")
         rng = np.random.Generator(np.random.Philox(np.random.SeedSequence([seed, idx])))
         t = torch.from_numpy(rng.standard_normal(shape, dtype=np.float32)) * std
         if init == "one_plus_normal":

@@ -84,6 +84,16 @@ def test_tensor_names_cache_entries_and_sizes_the_tensors_give():
     assert e.value.missing == ["l3.side.gate"] and e.value.wrong_shape == ["l0.mix.right.q"]
 
 
+def test_random_weights_need_the_sizes_the_tensors_would_give():
+    from pico_vllm_b200.errors import ConfigError
+    from pico_vllm_b200.weights import random_tensors
+    raw = copy.deepcopy(SHAPES["a"])
+    raw["layers"][0]["mixer"]["right"].pop("gate_rank")
+    with pytest.raises(ConfigError) as e:
+        random_tensors(_cfg(raw), 1)
+    assert "l0.mix.right.g1" in str(e.value)
+
+
 def test_random_weights_folder(tmp_path):
     from pico_vllm_b200.config.base import read_config_json
     from pico_vllm_b200.weights import write_random_model
