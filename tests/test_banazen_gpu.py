@@ -386,7 +386,8 @@ def _random_shape(seed):
     """A model whose every size, count, constant and order of layers is drawn from ``seed``."""
     import random
     rnd = random.Random(seed)
-    pick = rnd.choice
+    big = seed >= 8                           # from seed 8 on: heads of 128, latents of 256, more heads
+    pick = lambda xs: rnd.choice(xs + xs[-1:] * 3) if big else rnd.choice(xs)
     width = pick([64, 72, 96, 160, 320])
     n = rnd.randint(3, 6)
     layers, makers = [], []                   # makers: layers that make their own latents (index, rank)
@@ -395,20 +396,20 @@ def _random_shape(seed):
         if kind == "parallel":
             G = pick([1, 2, 3])
             H = G * pick([1, 2, 3])
-            d, dv = pick([16, 32, 64, 24]), pick([16, 32, 64, 40])
+            d, dv = pick([16, 32, 64, 24] + [128] * big), pick([16, 32, 64, 40] + [128] * big)
             rot = None if rnd.random() < 0.15 else (pick([100.0, 10000.0, 500000.0]), pick([d, d // 2, 8]))
             G2 = pick([1, 2, 4])
-            right = (G2 * pick([1, 2]), G2, pick([16, 32, 64, 48]), pick([16, 32, 64, 24]), rnd.randint(1, 4), rnd.randint(2, 12),
-                     rnd.randint(2, 12))
+            right = (G2 * pick([1, 2]), G2, pick([16, 32, 64, 48] + [128] * big), pick([16, 32, 64, 24] + [128] * big), rnd.randint(1, 4),
+                     rnd.randint(2, 12), rnd.randint(2, 12))
             mixer = _par((H, G, d, dv, pick([0.125, 0.2, d ** -0.5]), rnd.randint(1, 4), rot), right)
         else:
             window = pick([None, 5, 16, 33, 72, 100])
-            H, d, dv = rnd.randint(1, 8), pick([16, 32, 64, 24]), pick([16, 32, 64, 8])
+            H, d, dv = rnd.randint(1, 8) * (2 if big else 1), pick([16, 32, 64, 24] + [128] * big), pick([16, 32, 64, 8] + [128] * big)
             if kind == "from":
                 src, rank = pick(makers)
                 mixer = _lat(H, d, dv, rank, pick([0.125, 0.3]), window, kv_from=src)
             else:
-                rank = pick([32, 64, 96, 128, 40])
+                rank = pick([32, 64, 96, 128, 40] + [256] * big)
                 makers.append((i, rank))
                 mixer = _lat(H, d, dv, rank, pick([0.125, 0.3]), window)
         f = rnd.random()
@@ -429,9 +430,9 @@ def _random_shape(seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("seed", list(range(8)))
+@pytest.mark.parametrize("seed", list(range(12)))
 def test_drawn_shapes_in_mixed_batches(dtype, seed):
-    """Eight models drawn at random - sizes, head counts, order of layers, windows, taps, groups, constants - each with four
+    """Twelve models drawn at random - sizes, head counts, order of layers, windows, taps, groups, constants - each with four
     live requests, portions beside single tokens, pages and slots used again, against the plain implementation."""
     raw = _raw(_random_shape(seed), dtype)
     tensors = _tensors(raw, 100 + seed)
