@@ -23,9 +23,10 @@
 __device__ __forceinline__ float dr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float dr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// One block per token.  xc float32 [T, >= q_off.. ] holds the convolved q and k (G heads of d each); proj (activation
-// type) holds one beta logit per head at b_off; dt [T, H * d] (activation type) the decay's argument before its bias.
-// prep float32 [T, P] with P = 2 G d + H d + H + G:  q | k | a | beta | k . q.
+// Grid (tokens, 1 + H): block y = 0 makes the unit vectors and k . q of all query/key heads (a warp a head), block y = h + 1
+// the decays and beta of head h.  xc float32 [T, >= q_off.. ] holds the convolved q and k (G heads of d each); proj
+// (activation type) holds one beta logit per head at b_off; dt [T, H * d] (activation type) the decay's argument before
+// its bias.  prep float32 [T, P] with P = 2 G d + H d + H + G:  q | k | a | beta | k . q.
 template <typename TA>
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(const float* __restrict__ xc, int xc_stride, int q_off, int k_off, const TA* __restrict__ proj,
@@ -37,6 +38,16 @@ delta_prepare_kernel(const float* __restrict__ xc, int xc_stride, int q_off, int
     const size_t t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float* out = prep + t * P;
+    if (blockIdx.y > 0) {
+        const int h = blockIdx.y - 1;
+        const float rate = expf(a_log[h]);
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float z = to_f32(dt[t * dt_stride + h * d + i]) + (dt_bias ? dt_bias[h * d + i] : 0.f);
+            out[2 * G * d + h * d + i] = expf(-rate * dr_softplus(z));
+        }
+        if (threadIdx.x == 0) out[2 * G * d + H * d + h] = dr_sigmoid(to_f32(proj[t * proj_stride + b_off + h]));
+        return;
+    }
     const float* row = xc + t * xc_stride;
     for (int g = warp; g < G; g += nw) {
         float sq = 0.f, sk = 0.f;
@@ -58,13 +69,6 @@ delta_prepare_kernel(const float* __restrict__ xc, int xc_stride, int q_off, int
         kq = warp_sum(kq);
         if (lane == 0) out[2 * G * d + H * d + H + g] = kq;
     }
-    for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
-        const int h = i / d;
-        const float z = to_f32(dt[t * dt_stride + i]) + (dt_bias ? dt_bias[i] : 0.f);
-        out[2 * G * d + i] = expf(-expf(a_log[h]) * dr_softplus(z));
-    }
-    for (int h = threadIdx.x; h < H; h += blockDim.x)
-        out[2 * G * d + H * d + h] = dr_sigmoid(to_f32(proj[t * proj_stride + b_off + h]));
 }
 
 PICO_API int pico_delta_prepare(const float* xc, int xc_stride, int q_off, int k_off, const void* proj, int proj_stride,
@@ -72,14 +76,15 @@ PICO_API int pico_delta_prepare(const float* xc, int xc_stride, int q_off, int k
                                 float* prep, int T, int H, int G, int d, float q_scale, float unit_eps, int dtype,
                                 cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (H < 1 || G < 1 || H % G || d < 1) return PICO_ERR_SIZE;
+    if (H < 1 || G < 1 || H % G || d < 1 || H + 1 > 65535) return PICO_ERR_SIZE;
     const int P = 2 * G * d + H * d + H + G;
+    const dim3 grid(T, 1 + H);
     if (dtype == PICO_F32)
-        pico_launch((delta_prepare_kernel<float>), dim3(T), dim3(128), 0, stream, xc, xc_stride, q_off, k_off,
+        pico_launch((delta_prepare_kernel<float>), grid, dim3(128), 0, stream, xc, xc_stride, q_off, k_off,
                     (const float*)proj, proj_stride, b_off, (const float*)dt, dt_stride, dt_bias, a_log, prep, P, H, G, d,
                     q_scale, unit_eps);
     else if (dtype == PICO_BF16)
-        pico_launch((delta_prepare_kernel<bf16>), dim3(T), dim3(128), 0, stream, xc, xc_stride, q_off, k_off,
+        pico_launch((delta_prepare_kernel<bf16>), grid, dim3(128), 0, stream, xc, xc_stride, q_off, k_off,
                     (const bf16*)proj, proj_stride, b_off, (const bf16*)dt, dt_stride, dt_bias, a_log, prep, P, H, G, d,
                     q_scale, unit_eps);
     else
